@@ -1,0 +1,265 @@
+// Recurrent mixers of the ragged serving step: short causal convolutions with a carried tail, and linear-attention state
+// scans (a decayed outer-product state, and the gated delta rule), all in fp32.
+//
+// A step is a flat list of tokens; token t sits at position pos[t] of the sequence in state row slot[t]. The tokens of one
+// sequence are consecutive and form a run; `runs` int32 [n_runs, 4] = (first row, rows, position of the first row, state
+// row), or NULL: every token is a run of its own (a decode batch, read from pos / slot on the device). A run that starts
+// at position 0 starts from a zero state whatever its state row held before, so rows are reused without clearing.
+//
+//   b200_short_conv        y[t, c] = act(sum_j w[c, j] x[t - (taps - 1) + j, c]); inputs before the run come from the tail
+//                          kept in `state` [rows, taps - 1, C] (the last taps - 1 inputs; zeros before position 0).
+//   b200_short_conv_tail   advances that tail over the step's runs (launched after the convolution has read the old one).
+//   b200_delta_gates       q, k -> unit vectors per head (q also times `qscale`); a -> exp(-exp(A_log[h]) softplus(a + bias));
+//                          b -> sigmoid(b); in place, fp32.
+//   b200_linear_scan       per head, state S [D, Dv] (fp32, in `state` [rows, H, D, Dv]):
+//                            mode 0  S <- decay_h S + k v^T ;                                   o = S^T q
+//                            mode 1  S <- diag(g) S ; u = beta (v - S^T k) ; S <- S + k u^T ;   o = S^T q
+//                          Columns of S are independent, so a thread owns R rows of one column, the lanes that share a
+//                          column reduce their partial dot products by shuffles, and a CTA owns a block of columns of one
+//                          (run, head): tokens are walked in order, staged through shared memory in chunks.
+#include "common.cuh"
+#include "../include/b200_ops.h"
+
+namespace b200 {
+
+__device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); }
+
+__global__ void short_conv_kernel(const float* __restrict__ x, long long ldx, const float* __restrict__ w,
+                                  const float* __restrict__ state, const int* __restrict__ pos, const int* __restrict__ slot,
+                                  float* __restrict__ y, long long ldy, int tokens, int C, int taps, int act) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)tokens * C) return;
+  const int t = (int)(idx / C), c = (int)(idx % C);
+  const int p = pos[t], s = slot[t];
+  // nb: tokens of the same run right before t (at most taps - 1 matter)
+  int nb = 0;
+  while (nb < taps - 1 && t - nb - 1 >= 0 && slot[t - nb - 1] == s) ++nb;
+  float acc = 0.f;
+  for (int d = 0; d < taps; ++d) {                       // d tokens back
+    if (p - d < 0) break;
+    float v;
+    if (d <= nb) v = x[(long long)(t - d) * ldx + c];
+    else v = state[((long long)s * (taps - 1) + (taps - 1 - (d - nb))) * C + c];
+    acc = fmaf(w[(long long)c * taps + (taps - 1 - d)], v, acc);
+  }
+  y[(long long)t * ldy + c] = act ? silu_f(acc) : acc;
+}
+
+constexpr int kMaxTaps = 16;
+
+__global__ void short_conv_tail_kernel(const float* __restrict__ x, long long ldx, float* __restrict__ state,
+                                       const int* __restrict__ runs, const int* __restrict__ pos, const int* __restrict__ slot,
+                                       int n_runs, int C, int taps) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)n_runs * C) return;
+  const int r = (int)(idx / C), c = (int)(idx % C);
+  int first, n, p0, s;
+  if (runs) { first = runs[4 * r]; n = runs[4 * r + 1]; p0 = runs[4 * r + 2]; s = runs[4 * r + 3]; }
+  else { first = r; n = 1; p0 = pos[r]; s = slot[r]; }
+  const int L = taps - 1;
+  float* st = state + (long long)s * L * C + c;
+  float nv[kMaxTaps];
+  for (int i = 0; i < L; ++i) {
+    const int q = p0 + n - L + i;                        // position whose input lands in entry i
+    float v = 0.f;
+    if (q >= p0) v = x[(long long)(first + (q - p0)) * ldx + c];
+    else if (q >= 0) v = st[(long long)(q - p0 + L) * C];
+    nv[i] = v;
+  }
+  for (int i = 0; i < L; ++i) st[(long long)i * C] = nv[i];
+}
+
+// one warp per row of q / k / a, one thread per b
+__global__ void __launch_bounds__(128)
+delta_gates_kernel(float* __restrict__ q, long long ldq, float* __restrict__ k, long long ldk, float* __restrict__ a,
+                   long long lda, float* __restrict__ b, long long ldb, const float* __restrict__ dt_bias,
+                   const float* __restrict__ A_log, int G, int H, int D, float qscale, float unit_eps) {
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int r = warp; r < 2 * G + H; r += nw) {
+    if (r < 2 * G) {
+      float* x = r < G ? q + (long long)t * ldq + (long long)r * D : k + (long long)t * ldk + (long long)(r - G) * D;
+      float ss = 0.f;
+      for (int d = lane; d < D; d += 32) ss += x[d] * x[d];
+      ss = warp_sum(ss);
+      const float sc = rsqrtf(ss + unit_eps) * (r < G ? qscale : 1.f);
+      for (int d = lane; d < D; d += 32) x[d] *= sc;
+    } else {
+      const int h = r - 2 * G;
+      float* x = a + (long long)t * lda + (long long)h * D;
+      const float rate = expf(A_log[h]);
+      for (int d = lane; d < D; d += 32) {
+        const float z = x[d] + dt_bias[h * D + d];
+        const float sp = z > 20.f ? z : log1pf(expf(z));
+        x[d] = expf(-rate * sp);
+      }
+    }
+  }
+  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+    float* x = b + (long long)t * ldb + h;
+    *x = 1.f / (1.f + expf(-*x));
+  }
+}
+
+constexpr int kScanChunk = 16;
+
+// grid (runs, H, column blocks); block = NW warps; a warp covers 32 / LPC columns, lane = l * (32 / LPC) + jj
+template <int R, int MODE>
+__global__ void __launch_bounds__(128)
+linear_scan_kernel(const float* __restrict__ q, long long ldq, const float* __restrict__ k, long long ldk,
+                   const float* __restrict__ v, long long ldv, const float* __restrict__ g, long long ldg,
+                   const float* __restrict__ beta, long long ldb, const float* __restrict__ decay, float* __restrict__ state,
+                   const int* __restrict__ runs, const int* __restrict__ pos, const int* __restrict__ slot,
+                   float* __restrict__ o, int H, int G, int D, int Dv, int LPC, int act) {
+  extern __shared__ float sm[];
+  const int r_ = blockIdx.x, h = blockIdx.y;
+  int first, n, p0, s;
+  if (runs) { first = runs[4 * r_]; n = runs[4 * r_ + 1]; p0 = runs[4 * r_ + 2]; s = runs[4 * r_ + 3]; }
+  else { first = r_; n = 1; p0 = pos[r_]; s = slot[r_]; }
+  const int kvh = h / (H / G);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const int cpw = 32 / LPC;                               // columns per warp
+  const int l = lane / cpw, jj = lane % cpw;
+  const int ncol = nw * cpw;                              // columns per CTA
+  const int col0 = blockIdx.z * ncol;
+  const int j = col0 + warp * cpw + jj;
+  const bool live = j < Dv;
+  const int row0 = l * R;
+  const int DP = LPC * R;                                 // padded key size
+  float* ks = sm;                                         // [chunk][DP]
+  float* qs = ks + kScanChunk * DP;
+  float* gs = qs + kScanChunk * DP;                       // MODE 1 only
+  float* vs = gs + (MODE == 1 ? kScanChunk * DP : 0);     // [chunk][ncol]
+  float* bs = vs + kScanChunk * ncol;                     // [chunk]
+  float S[R];
+  float* sp = state + (((long long)s * H + h) * D) * Dv;
+#pragma unroll
+  for (int i = 0; i < R; ++i) S[i] = (p0 > 0 && live && row0 + i < D) ? sp[(long long)(row0 + i) * Dv + j] : 0.f;
+  const float dec = MODE == 0 ? decay[h] : 0.f;
+  for (int c0 = 0; c0 < n; c0 += kScanChunk) {
+    const int cn = min(kScanChunk, n - c0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < cn * DP; i += blockDim.x) {
+      const int tt = i / DP, d = i % DP;
+      const long long tr = first + c0 + tt;
+      float kv = 0.f, qv = 0.f, gv = 1.f;
+      if (d < D) {
+        kv = k[tr * ldk + (long long)kvh * D + d];
+        qv = q[tr * ldq + (long long)kvh * D + d];
+        if (act) { kv = silu_f(kv); qv = silu_f(qv); }
+        if (MODE == 1) gv = g[tr * ldg + (long long)h * D + d];
+      }
+      ks[i] = kv; qs[i] = qv;
+      if (MODE == 1) gs[i] = gv;
+    }
+    for (int i = threadIdx.x; i < cn * ncol; i += blockDim.x) {
+      const int tt = i / ncol, cc = i % ncol;
+      float vv = 0.f;
+      if (col0 + cc < Dv) { vv = v[(long long)(first + c0 + tt) * ldv + (long long)h * Dv + col0 + cc]; if (act) vv = silu_f(vv); }
+      vs[i] = vv;
+    }
+    if (MODE == 1) for (int i = threadIdx.x; i < cn; i += blockDim.x) bs[i] = beta[(long long)(first + c0 + i) * ldb + h];
+    __syncthreads();
+    for (int tt = 0; tt < cn; ++tt) {
+      const float* kr = ks + tt * DP + row0;
+      const float* qr = qs + tt * DP + row0;
+      const float vj = vs[tt * ncol + warp * cpw + jj];
+      float oacc = 0.f;
+      if (MODE == 0) {
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+          S[i] = fmaf(dec, S[i], kr[i] * vj);
+          oacc = fmaf(S[i], qr[i], oacc);
+        }
+      } else {
+        const float* gr = gs + tt * DP + row0;
+        float dot = 0.f;
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+          S[i] *= gr[i];
+          dot = fmaf(S[i], kr[i], dot);
+        }
+        for (int x = cpw; x < 32; x <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, x);
+        const float u = bs[tt] * (vj - dot);
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+          S[i] = fmaf(kr[i], u, S[i]);
+          oacc = fmaf(S[i], qr[i], oacc);
+        }
+      }
+      for (int x = cpw; x < 32; x <<= 1) oacc += __shfl_xor_sync(0xffffffffu, oacc, x);
+      if (l == 0 && live) o[((long long)(first + c0 + tt) * H + h) * Dv + j] = oacc;
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < R; ++i)
+      if (row0 + i < D) sp[(long long)(row0 + i) * Dv + j] = S[i];
+  }
+}
+}  // namespace b200
+
+B200_API int b200_short_conv(const float* x, long long ldx, const float* w, const float* state, const int* pos, const int* slot,
+                             float* y, long long ldy, int tokens, int C, int taps, int act, void* stream) {
+  using namespace b200;
+  if (tokens <= 0) return 0;
+  if (C <= 0 || taps < 1 || taps > kMaxTaps) return B200_ERR_BAD_SHAPE;
+  const long long n = (long long)tokens * C;
+  short_conv_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, ldx, w, state, pos, slot, y, ldy, tokens, C, taps, act);
+  B200_LAUNCH_CHECK();
+  return 0;
+}
+
+B200_API int b200_short_conv_tail(const float* x, long long ldx, float* state, const int* runs, const int* pos, const int* slot,
+                                  int n_runs, int C, int taps, void* stream) {
+  using namespace b200;
+  if (n_runs <= 0 || taps <= 1) return 0;
+  if (C <= 0 || taps > kMaxTaps) return B200_ERR_BAD_SHAPE;
+  const long long n = (long long)n_runs * C;
+  short_conv_tail_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, ldx, state, runs, pos, slot, n_runs, C, taps);
+  B200_LAUNCH_CHECK();
+  return 0;
+}
+
+B200_API int b200_delta_gates(float* q, long long ldq, float* k, long long ldk, float* a, long long lda, float* b, long long ldb,
+                              const float* dt_bias, const float* A_log, int tokens, int G, int H, int D, float qscale,
+                              float unit_eps, void* stream) {
+  using namespace b200;
+  if (tokens <= 0) return 0;
+  delta_gates_kernel<<<tokens, 128, 0, (cudaStream_t)stream>>>(q, ldq, k, ldk, a, lda, b, ldb, dt_bias, A_log, G, H, D, qscale, unit_eps);
+  B200_LAUNCH_CHECK();
+  return 0;
+}
+
+B200_API int b200_linear_scan(const float* q, long long ldq, const float* k, long long ldk, const float* v, long long ldv,
+                              const float* g, long long ldg, const float* beta, long long ldb, const float* decay, float* state,
+                              const int* runs, const int* pos, const int* slot, int n_runs, float* o, int H, int G, int D, int Dv,
+                              int mode, int act, void* stream) {
+  using namespace b200;
+  if (n_runs <= 0) return 0;
+  if (H <= 0 || G <= 0 || H % G || D <= 0 || Dv <= 0 || mode < 0 || mode > 1 || H > 65535) return B200_ERR_BAD_SHAPE;
+  // rows per thread R in {8, 16, 32}; lanes per column LPC = power of two with LPC * R >= D
+  int R = D <= 8 ? 8 : (D <= 256 ? 16 : 32);
+  int LPC = 1;
+  while (LPC * R < D) LPC *= 2;
+  if (LPC > 32) return B200_ERR_TOO_LARGE;
+  const int cpw = 32 / LPC;
+  int nw = 4;
+  while (nw > 1 && (nw - 1) * cpw >= Dv) --nw;            // no warp without columns
+  const int ncol = nw * cpw;
+  const int zb = (Dv + ncol - 1) / ncol;
+  const int DP = LPC * R;
+  const size_t smem = ((size_t)kScanChunk * DP * (mode == 1 ? 3 : 2) + (size_t)kScanChunk * ncol + kScanChunk) * 4;
+  if (smem > 48 * 1024) return B200_ERR_TOO_LARGE;
+  dim3 grid(n_runs, H, zb);
+  cudaStream_t st = (cudaStream_t)stream;
+#define SCAN(RR)                                                                                                           \
+  do {                                                                                                                     \
+    if (mode == 0) linear_scan_kernel<RR, 0><<<grid, nw * 32, smem, st>>>(q, ldq, k, ldk, v, ldv, g, ldg, beta, ldb, decay, state, runs, pos, slot, o, H, G, D, Dv, LPC, act); \
+    else linear_scan_kernel<RR, 1><<<grid, nw * 32, smem, st>>>(q, ldq, k, ldk, v, ldv, g, ldg, beta, ldb, decay, state, runs, pos, slot, o, H, G, D, Dv, LPC, act); \
+  } while (0)
+  if (R == 8) SCAN(8); else if (R == 16) SCAN(16); else SCAN(32);
+#undef SCAN
+  B200_LAUNCH_CHECK();
+  return 0;
+}

@@ -526,6 +526,54 @@ int b200_latent_attn_mma(const void* q, const void* cache, const int* tiles, int
 int b200_gemm_f32_exact(const float* A, const float* B, float* D, int M, int N, int K, long long lda, long long ldb, long long ldd,
                         void* stream);
 
+/* ---- hyper-connected residual streams, xIELU, gated group norm (csrc/hyper_conn.cu) ----
+ * X fp32 [tokens, S, W] (S <= 8). mode 0: x_t <- sum_s mix[s, t] x_s + out[t] * ls * y (y fp32 [tokens, W]; ls fp32 [W] or
+ * NULL), then u = sum_s in_next[s] x_s (NULL: ones) and h = u / sqrt(mean(u^2) + eps) * g_next[0] (h NULL: no read).
+ * mode 1: y holds embedding rows (e_dtype) that are normed with g_entry[0] and copied into every stream first; mode 2: read
+ * only. xsum: optional fp32 [tokens, W] that receives the sum of the streams. */
+int b200_hc_step(const void* y, const float* ls, float* X, const float* mix, const float* outc, const float* g_entry,
+                 const float* in_next, const float* g_next, void* h, float* xsum, long long tokens, int S, int W, float eps,
+                 int mode, int h_dtype, int e_dtype, void* stream);
+/* y = xIELU(z) with raw parameters pq = (p, q) on the device: z > 0: softplus(p) z^2 + z / 2, else
+ * (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2. */
+int b200_xielu(const void* z, void* y, long long n, const float* pq, int dtype, void* stream);
+/* out [tokens, NG, GS] = o / sqrt(mean over a group (o^2) + eps) * w[GS] * sigmoid(gate) (gate fp32 rows of ld_gate, or NULL). */
+int b200_gated_group_norm(const float* o, const float* gate, long long ld_gate, const float* w, void* out, long long tokens,
+                          int NG, int GS, float eps, int dtype, void* stream);
+
+/* ---- multi-map (differential) attention with a sliding window that keeps the first tokens (csrc/multimap_attn.cu) ----
+ * proj fp32 [tokens, ld] = H * M query rows of D | (has_kv) G * M key rows of D | G value rows of Dv. Every q / k row is
+ * RMS-normed over D with wq / wk (fp32 [D]), its first `rot` dims turn by the token's position (dim i pairs with
+ * i + rot / 2; cos / sin fp32 [max_pos, rot / 2]); q -> q_out [tokens, H * M * D], k -> ck [blocks, G * M, block_size, D],
+ * v -> cv [blocks, G, block_size, Dv]. */
+int b200_qknorm_rope_store(const float* proj, long long ld, const float* wq, const float* wk, const float* cos_t,
+                           const float* sin_t, const int* pos, const int* slot, const int* table, int max_blocks, void* q_out,
+                           void* ck, void* cv, int tokens, int H, int G, int M, int D, int Dv, int rot, int block_size, float eps,
+                           int has_kv, int dtype, void* stream);
+/* out [tokens, H * Dv]: token t sees key j <= pos[t] of its row if pos[t] - j < window or j < keep_first (window <= 0: all).
+ * Each of the M maps is a softmax attention over the same values; combine (M = 2): o = a_0 - lambda a_1, then
+ * o / sqrt(mean(o^2) + eps) * post. Dv <= 256. fp32 arithmetic. */
+int b200_multimap_attn(const void* q, const void* ck, const void* cv, const int* pos, const int* slot, const int* table,
+                       int max_blocks, void* out, int tokens, int H, int G, int M, int D, int Dv, int block_size, float scale,
+                       int window, int keep_first, int combine, float lambda, float post, float eps, int dtype, void* stream);
+
+/* ---- recurrent mixers of the ragged step (csrc/linear_scan.cu); runs int32 [n_runs, 4] = (first row, rows, first position,
+ * state row) or NULL (every token its own run, from pos / slot). A run at position 0 starts from zero state. ---- */
+int b200_short_conv(const float* x, long long ldx, const float* w, const float* state, const int* pos, const int* slot, float* y,
+                    long long ldy, int tokens, int C, int taps, int act, void* stream);
+int b200_short_conv_tail(const float* x, long long ldx, float* state, const int* runs, const int* pos, const int* slot, int n_runs,
+                         int C, int taps, void* stream);
+int b200_delta_gates(float* q, long long ldq, float* k, long long ldk, float* a, long long lda, float* b, long long ldb,
+                     const float* dt_bias, const float* A_log, int tokens, int G, int H, int D, float qscale, float unit_eps,
+                     void* stream);
+/* mode 0: S <- decay[h] S + k v^T; mode 1: S <- diag(g) S, u = beta (v - S^T k), S <- S + k u^T; o = S^T q (fp32
+ * [tokens, H, Dv]). q / k have G heads of D (head h reads h / (H / G)), v H heads of Dv, g [tokens, H * D], beta [tokens, H].
+ * act 1: silu on q, k, v as they are read. state fp32 [rows, H, D, Dv]. */
+int b200_linear_scan(const float* q, long long ldq, const float* k, long long ldk, const float* v, long long ldv, const float* g,
+                     long long ldg, const float* beta, long long ldb, const float* decay, float* state, const int* runs,
+                     const int* pos, const int* slot, int n_runs, float* o, int H, int G, int D, int Dv, int mode, int act,
+                     void* stream);
+
 #ifdef __cplusplus
 }
 #endif

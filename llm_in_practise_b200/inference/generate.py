@@ -99,7 +99,8 @@ class PagedKVCache(KVCache):
     (serve/engine.py); this class only holds the storage and the table."""
     paged = True
 
-    def __init__(self, n_layers, num_blocks, Hkv, block_size, D, dtype, device, max_seqs, max_len, Dv=None):
+    def __init__(self, n_layers, num_blocks, Hkv, block_size, D, dtype, device, max_seqs, max_len, Dv=None, Hv=None,
+                 state_shapes=None):
         if block_size & (block_size - 1):
             raise ValueError("block_size must be a power of two")
         # Hkv / D may be lists: models whose layers differ in their KV heads or head size get one pool per layer. Dv: the value
@@ -108,8 +109,15 @@ class PagedKVCache(KVCache):
         hk = list(Hkv) if isinstance(Hkv, (list, tuple)) else [Hkv] * n_layers
         hd = list(D) if isinstance(D, (list, tuple)) else [D] * n_layers
         hv = hd if Dv is None else (list(Dv) if isinstance(Dv, (list, tuple)) else [Dv] * n_layers)
+        # Hv: value heads per layer where they differ from the key rows (layers with several key rows per value head).
+        # A layer with 0 key heads holds no pool of its own (it reads another layer's, or it is not an attention layer)
+        gv = hk if Hv is None else list(Hv)
         self.k = [torch.zeros(num_blocks, hk[i], block_size, hd[i], dtype=dtype, device=device) for i in range(n_layers)]
-        self.v = [torch.zeros(num_blocks, hk[i], block_size, hv[i], dtype=dtype, device=device) for i in range(n_layers)]
+        self.v = [torch.zeros(num_blocks, gv[i], block_size, hv[i], dtype=dtype, device=device) for i in range(n_layers)]
+        # state_shapes: per layer, the shapes of the fp32 tensors a recurrent mixer carries from token to token for each
+        # sequence; row r of state[layer][i] belongs to the sequence in table row r (slots are the unit of allocation)
+        self.state = [[torch.zeros(max_seqs, *shp, dtype=torch.float32, device=device) for shp in (state_shapes[i] if state_shapes else [])]
+                      for i in range(n_layers)]
         self.block_size, self.num_blocks = block_size, num_blocks
         self.max_len = max_len
         self.max_blocks = -(-max_len // block_size)

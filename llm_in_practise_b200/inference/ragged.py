@@ -32,6 +32,8 @@ class Pieces:
     tiles: torch.Tensor
     n_tiles: int
     longest: int                    # tokens of the longest run
+    runs: Optional[torch.Tensor] = None     # int32 [n_runs, 4] = (first row, rows, position of the first row, cache row): whole runs,
+    n_runs: int = 0                         # walked in order by the recurrent mixers (ops.linear_scan)
 
     def use_mma(self, q: torch.Tensor, head_dim: int, window: int, scale: float = 1.0) -> bool:
         return (self.longest >= 8 and scale > 0 and q.dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 128
@@ -54,19 +56,36 @@ class RaggedGenerator(Generator):
         is left to unset table entries; callers hand out blocks 1 .. num_blocks."""
         m = self.model
         lay = self._kv_layout()
-        cache = PagedKVCache(len(lay), num_blocks + 1, [g for g, _, _ in lay], block_size, [d for _, d, _ in lay], m.embed_tokens.dtype,
-                             m.embed_tokens.device, max_seqs + 1, max_len, Dv=[dv for _, _, dv in lay])
+        states = m.state_layout() if hasattr(m, "state_layout") else None
+        cache = PagedKVCache(len(lay), num_blocks + 1, [e[0] for e in lay], block_size, [e[1] for e in lay], m.embed_tokens.dtype,
+                             m.embed_tokens.device, max_seqs + 1, max_len, Dv=[e[2] for e in lay], Hv=[e[3] for e in lay],
+                             state_shapes=states)
         cache.scratch_row = max_seqs             # a row that never gets blocks: padding tokens of a bucketed batch write to block 0
         return cache
 
     def _kv_layout(self):
-        """(kv heads, key row size, value row size) per layer; a model's ``kv_layout`` may give pairs (values sized like keys)
-        or triples (value size 0: the layer keeps no value pool, e.g. a latent cache whose rows serve as both)."""
-        return [(e[0], e[1], e[2] if len(e) > 2 else e[1]) for e in self.model.kv_layout()]
+        """(key rows per token, key row size, value row size, value heads) per layer; a model's ``kv_layout`` may give pairs
+        (values sized like keys), triples (value size 0: the layer keeps no value pool, e.g. a latent cache whose rows serve
+        as both) or all four (several key rows per value head; 0 key rows: the layer has no pool of its own)."""
+        return [(e[0], e[1], e[2] if len(e) > 2 else e[1], e[3] if len(e) > 3 else e[0]) for e in self.model.kv_layout()]
 
     def kv_token_bytes(self) -> int:
         es = self.model.embed_tokens.element_size()
-        return sum(g * (d + dv) * es for g, d, dv in self._kv_layout())
+        return sum((g * d + gv * dv) * es for g, d, dv, gv in self._kv_layout())
+
+    def state_bytes(self) -> int:
+        """Bytes of recurrent state one live sequence holds (fp32), over all layers."""
+        m = self.model
+        if not hasattr(m, "state_layout"):
+            return 0
+        n = 0
+        for shapes in m.state_layout():
+            for shp in shapes:
+                k = 4
+                for d in shp:
+                    k *= d
+                n += k
+        return n
 
     # ------------------------------------------------------------------ the step
     @torch.no_grad()
@@ -83,6 +102,7 @@ class RaggedGenerator(Generator):
         slot: List[int] = []
         want: List[int] = []
         tiles: List[List[int]] = []
+        runs: List[List[int]] = []
         longest = max_pos = 0
         for row, pos0, toks, wanted in entries:
             n = len(toks)
@@ -95,6 +115,7 @@ class RaggedGenerator(Generator):
             pos.extend(range(pos0, pos0 + n))
             slot.extend([row] * n)
             want.extend(base + int(w) for w in wanted)
+            runs.append([base, n, pos0, row])
             for q0 in range(0, n, TILE_Q):
                 tiles.append([base + q0, min(TILE_Q, n - q0), pos0 + q0, row])
             longest = max(longest, n)
@@ -105,11 +126,11 @@ class RaggedGenerator(Generator):
         if dev.type == "cuda":
             meta = meta.pin_memory().to(dev, non_blocking=True)
             ids_t = torch.tensor(ids, dtype=torch.long).pin_memory().to(dev, non_blocking=True)
-            tl = torch.tensor(tiles, dtype=torch.int32).pin_memory().to(dev, non_blocking=True)
+            tl = torch.tensor(tiles + runs, dtype=torch.int32).pin_memory().to(dev, non_blocking=True)
         else:
             ids_t = torch.tensor(ids, dtype=torch.long)
-            tl = torch.tensor(tiles, dtype=torch.int32)
-        pieces = Pieces(tl, len(tiles), longest)
+            tl = torch.tensor(tiles + runs, dtype=torch.int32)
+        pieces = Pieces(tl[:len(tiles)], len(tiles), longest, tl[len(tiles):], len(runs))
         want_t = torch.tensor(want, dtype=torch.long, device=dev) if want else torch.zeros(1, dtype=torch.long, device=dev)
         logits = self.model.forward_ragged(ids_t, meta[0], meta[1], cache, want_t, max_pos=max_pos, pieces=pieces,
                                            layer_outputs=layer_outputs)

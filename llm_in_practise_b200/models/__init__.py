@@ -16,6 +16,11 @@ def _load_segorax(path, dtype, device):
     return segorax_from_pretrained(path, dtype=dtype, device=device)
 
 
+def _load_duratar(path, dtype, device):
+    from .duratar import duratar_from_pretrained
+    return duratar_from_pretrained(path, dtype=dtype, device=device)
+
+
 # ``architecture`` (or HF ``model_type`` / ``architectures[0]``) of config.json -> loader(path, dtype, device).
 # Anything not listed is read as a Qwen2/Qwen3-style HF checkpoint by ``io.hf.from_pretrained``.
 MODEL_REGISTRY: Dict[str, Callable] = {
@@ -23,6 +28,8 @@ MODEL_REGISTRY: Dict[str, Callable] = {
     "gorozen": _load_gorozen,
     "Segorax": _load_segorax,
     "segorax": _load_segorax,
+    "Duratar": _load_duratar,
+    "duratar": _load_duratar,
 }
 
 

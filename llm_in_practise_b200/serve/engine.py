@@ -132,10 +132,17 @@ class LLMEngine:
         if self.ragged and self.args.block_size <= 0:
             self.args.block_size = 64                    # the ragged step reads K/V through a block table only
         if self.ragged:
+            state_bytes = self.gen.state_bytes()
+            if state_bytes and (self.args.enable_prefix_caching or self.args.kv_offload_gb):
+                # a recurrent mixer's state summarises the whole prefix: the K/V blocks of a finished sequence cannot
+                # restart another one in the middle, so rows of finished sequences are not kept for such models
+                self.args.enable_prefix_caching = False
+                self.args.kv_offload_gb = 0.0
             if self.args.gpu_memory_utilization > 0 and self.device.type == "cuda":
                 free, total = torch.cuda.mem_get_info(self.device)
                 budget = free - (1.0 - self.args.gpu_memory_utilization) * total
-                self.args.max_num_seqs = int(max(1, min(4096, budget // (self.gen.kv_token_bytes() * self.args.max_model_len) - 1)))
+                per_seq = self.gen.kv_token_bytes() * self.args.max_model_len + state_bytes
+                self.args.max_num_seqs = int(max(1, min(4096, budget // per_seq - 1)))
         elif self.args.gpu_memory_utilization > 0 and self.device.type == "cuda":
             # vLLM's knob: the KV pool takes what is left of `utilization x total HBM` after the weights
             free, total = torch.cuda.mem_get_info(self.device)
