@@ -556,6 +556,12 @@ int b200_qknorm_rope_store(const float* proj, long long ld, const float* wq, con
 int b200_multimap_attn(const void* q, const void* ck, const void* cv, const int* pos, const int* slot, const int* table,
                        int max_blocks, void* out, int tokens, int H, int G, int M, int D, int Dv, int block_size, float scale,
                        int window, int keep_first, int combine, float lambda, float post, float eps, int dtype, void* stream);
+/* The same for bf16 prompt pieces on mma.sync: tiles int32 [n_tiles, 4] = (first row, rows <= 64, position of the first row,
+ * cache row). D in {32, 48, 64, 96, 128}, Dv in {32, 64, 96, 128}, block_size a power of two, scale > 0; else
+ * B200_ERR_UNSUPPORTED (use b200_multimap_attn). */
+int b200_multimap_attn_mma(const void* q, const void* ck, const void* cv, const int* tiles, int n_tiles, const int* table,
+                           int max_blocks, void* out, int H, int G, int M, int D, int Dv, int block_size, float scale, int window,
+                           int keep_first, int combine, float lambda, float post, float eps, int dtype, void* stream);
 
 /* ---- recurrent mixers of the ragged step (csrc/linear_scan.cu); runs int32 [n_runs, 4] = (first row, rows, first position,
  * state row) or NULL (every token its own run, from pos / slot). A run at position 0 starts from zero state. ---- */

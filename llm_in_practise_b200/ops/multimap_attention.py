@@ -15,6 +15,7 @@ the same ragged step (the reference reaches it through vLLM, LLM_on_Kubernetes/I
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -22,6 +23,7 @@ import torch
 from . import _native as nv
 
 vp, i32, i64, f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+_MMA_D, _MMA_DV = (32, 48, 64, 96, 128), (32, 64, 96, 128)        # sizes the tensor-core kernel is built for
 
 
 def qknorm_rope_store(proj: torch.Tensor, wq: torch.Tensor, wk: Optional[torch.Tensor], cos: torch.Tensor, sin: torch.Tensor,
@@ -47,7 +49,7 @@ def qknorm_rope_store(proj: torch.Tensor, wq: torch.Tensor, wk: Optional[torch.T
         return q_out
     pl, sl = pos.long(), slot.long()
     hr = rot // 2
-    c, s = cos[pl][:, None, :], sin[pl][:, None, :]
+    c, s = (cos[pl][:, None, :], sin[pl][:, None, :]) if rot else (None, None)
 
     def prep(x, w):
         x = x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * w.float()
@@ -74,13 +76,23 @@ def multimap_attention(q: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Te
                        keep_first: int = 0, combine: bool = False, lam: float = 0.0, post: float = 1.0, eps: float = 0.0,
                        pieces=None) -> torch.Tensor:
     """Context [T, H * Dv] (q's dtype) of ``q`` [T, H * M * D] over the pools; see the module docstring for the mask and the
-    combination. Prompt pieces and single decoded tokens take the same kernel."""
+    combination. ``pieces`` (``inference.ragged.Pieces``): bf16 steps with a run of 8 or more tokens go through the tensor-core
+    kernel; everything else (fp32, decode batches, sizes it is not built for) through the per-(token, head) kernel."""
     T = q.shape[0]
     BS = cache_k.shape[2]
     out = torch.empty(T, H * Dv, dtype=q.dtype, device=q.device)
     if nv.use_native(q):
         if cache_k.dtype != q.dtype or not q.is_contiguous():
             raise ValueError("multimap_attention: contiguous q in the cache dtype")
+        if (pieces is not None and pieces.longest >= 8 and q.dtype == torch.bfloat16 and D in _MMA_D and Dv in _MMA_DV and scale > 0
+                and BS & (BS - 1) == 0 and os.environ.get("B200_PAGED_MMA", "1") != "0"):
+            fn = nv.proto("b200_multimap_attn_mma", [vp, vp, vp, vp, i32, vp, i32, vp, i32, i32, i32, i32, i32, i32, f32, i32, i32, i32,
+                                                     f32, f32, f32, i32, vp])
+            nv.check(fn(nv.ptr(q), nv.ptr(cache_k), nv.ptr(cache_v), nv.ptr(pieces.tiles), pieces.n_tiles, nv.ptr(table),
+                        table.shape[1], nv.ptr(out), H, G, M, D, Dv, BS, float(scale), int(window), int(keep_first), int(combine),
+                        float(lam), float(post), float(eps), nv.dtype_code(q.dtype), nv.stream()), "multimap_attn_mma")
+            nv.count_launch()
+            return out
         fn = nv.proto("b200_multimap_attn", [vp, vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, i32, f32, i32, i32, i32,
                                              f32, f32, f32, i32, vp])
         nv.check(fn(nv.ptr(q), nv.ptr(cache_k), nv.ptr(cache_v), nv.ptr(pos), nv.ptr(slot), nv.ptr(table), table.shape[1],

@@ -23,7 +23,8 @@ import sys
 NATIVE_SOURCES = {
     "Gorozen": ["gemm_tcgen05", "gemv", "gemm_simt", "norm", "elementwise", "paged_attn", "moe"],
     "Segorax": ["gemm_tcgen05", "gemv", "gemm_simt", "norm", "elementwise", "latent_attn", "moe"],
-    "Duratar": ["gemm_tcgen05", "gemv", "gemm_simt", "elementwise", "hyper_conn", "multimap_attn", "linear_scan"],
+    "Duratar": ["gemm_tcgen05", "gemv", "gemm_simt", "elementwise", "hyper_conn", "multimap_attn", "multimap_attn_mma",
+                "linear_scan"],
 }
 BLOCK = 64
 MAX_LIVE = 4

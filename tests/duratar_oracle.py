@@ -88,28 +88,39 @@ def attention_keys(m, w, pre, h, eps):
     return k, v
 
 
+def attend(q, k, v, scale, size, keep, lam, diff, eps):
+    """q [T, H, 2, D], k [T, G, 2, D], v [T, G, Dv] of one sequence from position 0 -> [T, H, Dv]: two softmax maps per head
+    over the visible keys, combined as a_1 - lam a_2, divided by the root mean square over Dv, times (1 - diff)."""
+    T, H = q.shape[:2]
+    G, Dv = v.shape[1:]
+    rep = H // G
+    out = torch.zeros(T, H, Dv, dtype=F64)
+    for i in range(T):
+        js = [j for j in range(i + 1) if visible(i, j, size, keep)]
+        kk = k[js].repeat_interleave(rep, 1)                       # [n, H, 2, D]
+        vv = v[js].repeat_interleave(rep, 1)                       # [n, H, Dv]
+        sc = torch.einsum("hmd,nhmd->hmn", q[i], kk) * scale
+        a = torch.einsum("hmn,nhe->hme", torch.softmax(sc, -1), vv)
+        out[i] = rms(a[:, 0] - lam * a[:, 1], eps) * (1 - diff)
+    return out
+
+
+def diff_lambda(m, w, pre):
+    return (math.exp(float((f64(w[pre + "lq1"]) * f64(w[pre + "lk1"])).sum()))
+            - math.exp(float((f64(w[pre + "lq2"]) * f64(w[pre + "lk2"])).sum())) + m["diff"])
+
+
 def attention(m, w, pre, h, eps, shared=None):
     T = h.shape[0]
-    H, G, D, Dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    H, D = m["heads"], m["dim"]
     q = (h @ f64(w[pre + "q"]).T).view(T, H, 2, D)
     q = rms(q, eps) * f64(w[pre + "q.norm"])
     fr = rope_freqs(m["rot"]["dims"], m["rot"]["base"], m["rot"].get("scaling"))
     q = torch.stack([rotate_half(q[t], t, fr) for t in range(T)])
     k, v = shared if shared is not None else attention_keys(m, w, pre, h, eps)
-    lam = (math.exp(float((f64(w[pre + "lq1"]) * f64(w[pre + "lk1"])).sum()))
-           - math.exp(float((f64(w[pre + "lq2"]) * f64(w[pre + "lk2"])).sum())) + m["diff"])
-    size, keep = m["mask"]["size"], m["mask"]["keep_first"]
-    out = torch.zeros(T, H, Dv, dtype=F64)
-    rep = H // G
-    for i in range(T):
-        js = [j for j in range(i + 1) if visible(i, j, size, keep)]
-        kk = k[js].repeat_interleave(rep, 1)                       # [n, H, 2, D]
-        vv = v[js].repeat_interleave(rep, 1)                       # [n, H, Dv]
-        sc = torch.einsum("hmd,nhmd->hmn", q[i], kk) * m["scale"]
-        a = torch.einsum("hmn,nhe->hme", torch.softmax(sc, -1), vv)
-        o = a[:, 0] - lam * a[:, 1]
-        out[i] = rms(o, eps) * (1 - m["diff"])
-    return out.reshape(T, H * Dv) @ f64(w[pre + "o"]).T, (k, v)
+    size = m["mask"]["size"] if m["mask"].get("size") else 1 << 60
+    out = attend(q, k, v, m["scale"], size, m["mask"].get("keep_first", 0), diff_lambda(m, w, pre), m["diff"], eps)
+    return out.reshape(T, -1) @ f64(w[pre + "o"]).T, (k, v)
 
 
 def lightning(m, w, pre, h, eps):
@@ -219,3 +230,97 @@ def forward(cfg, w, tokens, layer_outputs=None):
             layer_outputs.append(sum(xs))
     x = sum(xs)
     return scalar_norm(x, w["final.norm"], eps) @ f64(w["head"]).T
+
+
+def greedy(cfg, w, prompt, new):
+    toks = list(prompt)
+    for _ in range(new):
+        toks.append(int(forward(cfg, w, toks)[-1].argmax()))
+    return toks
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# small configurations and random weights for the tests
+# ----------------------------------------------------------------------------------------------------------------------
+def attention_layer(heads, kv_heads, dim, vdim, size, keep, rot_dims, base=10000.0, scaling=None, diff=0.3, scale=None, kv_from=None,
+                    ff=0):
+    m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "diff": diff, "scale": scale if scale is not None else 0.6,
+         "mask": {"size": size, "keep_first": keep}, "rot": {"base": base, "dims": rot_dims}}
+    if scaling:
+        m["rot"]["scaling"] = scaling
+    if kv_from is not None:
+        m["kv_from"] = kv_from
+    return {"type": "attention", "mixer": m, "mlp": {"kind": "dense", "ff": ff} if ff else None}
+
+
+def lightning_layer(heads, dim, vdim, decay, ff=0):
+    return {"type": "lightning", "mixer": {"heads": heads, "dim": dim, "vdim": vdim, "decay": list(decay)},
+            "mlp": {"kind": "dense", "ff": ff} if ff else None}
+
+
+def delta_layer(heads, kv_heads, dim, vdim, conv, ff=0):
+    return {"type": "channel_delta", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv},
+            "mlp": {"kind": "dense", "ff": ff} if ff else None}
+
+
+def make_config(width, vocab, layers, streams=2, eps=1e-5):
+    cfg = {"architecture": "Duratar", "vocab": vocab, "width": width, "norm": {"eps": eps}, "layers": layers}
+    if streams is not None:
+        cfg["streams"] = streams
+    return cfg
+
+
+def random_weights(cfg, seed=0, ranks=(12, 8), dtype=torch.bfloat16):
+    """Weights under the checkpoint's names, rounded to ``dtype`` (the oracle and the package read the same numbers)."""
+    g = torch.Generator().manual_seed(seed)
+    W, V = cfg["width"], cfg["vocab"]
+    S = cfg.get("streams", 1)
+    w = {}
+    rn = lambda *shape, std=1.0, mean=0.0: (torch.randn(tuple(shape), generator=g) * std + mean)      # noqa: E731
+    lin = lambda o, i, gain=1.0: rn(o, i, std=gain * i ** -0.5)                                  # noqa: E731
+    w["embed"] = rn(V, W)
+    w["embed.norm"] = rn(std=0.1, mean=1.2)
+    w["final.norm"] = rn(std=0.1, mean=0.9)
+    w["head"] = lin(V, W)
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        for q in (1, 2) if L.get("mlp") else (1,):
+            w[f"{p}norm{q}"] = rn(std=0.2, mean=1.0)
+            w[f"{p}ls{q}"] = rn(W, std=0.3, mean=0.8)
+            if "streams" in cfg:
+                w[f"{p}hc{q}.in"] = rn(S, std=0.4, mean=0.7)
+                w[f"{p}hc{q}.out"] = rn(S, std=0.4, mean=0.8)
+                w[f"{p}hc{q}.mix"] = torch.eye(S) * 0.9 + rn(S, S, std=0.25)
+        H, D, Dv = m["heads"], m["dim"], m["vdim"]
+        x = p + "mix."
+        if L["type"] == "attention":
+            G = m["kv_heads"]
+            w[x + "q"] = lin(H * 2 * D, W)
+            w[x + "q.norm"] = rn(D, std=0.3, mean=1.0)
+            if m.get("kv_from") is None:
+                w[x + "k"] = lin(G * 2 * D, W)
+                w[x + "v"] = lin(G * Dv, W)
+                w[x + "k.norm"] = rn(D, std=0.3, mean=1.0)
+            for n in ("lq1", "lk1", "lq2", "lk2"):
+                w[x + n] = rn(D, std=0.25)
+        elif L["type"] == "lightning":
+            for n, r in (("q", H * D), ("k", H * D), ("v", H * Dv), ("g", H * Dv)):
+                w[x + n] = lin(r, W, 1.5)
+            w[x + "norm"] = rn(H * Dv, std=0.3, mean=1.0)
+        else:
+            G = m["kv_heads"]
+            for n, r in (("q", G * D), ("k", G * D), ("v", H * Dv)):
+                w[x + n] = lin(r, W, 1.5)
+                w[x + n + ".conv"] = rn(r, m["conv"], std=0.6)
+            w[x + "b"] = lin(H, W, 2.0)
+            w[x + "A_log"] = rn(H, std=0.7)
+            w[x + "dt_bias"] = rn(H * D, std=1.0)
+            w[x + "norm"] = rn(Dv, std=0.3, mean=1.0)
+            w[x + "a1"], w[x + "a2"] = lin(ranks[0], W), lin(H * D, ranks[0], 2.0)
+            w[x + "g1"], w[x + "g2"] = lin(ranks[1], W), lin(H * Dv, ranks[1], 2.0)
+        w[x + "o"] = lin(W, H * Dv)
+        if L.get("mlp"):
+            F = L["mlp"]["ff"]
+            w[p + "mlp.up"], w[p + "mlp.down"] = lin(F, W), lin(W, F)
+            w[p + "mlp.act"] = rn(2, std=0.7)
+    return {k: v.to(dtype) for k, v in w.items()}
