@@ -80,16 +80,23 @@ hc_step_kernel(const void* __restrict__ y_, const float* __restrict__ ls, float*
 }
 
 // xIELU with raw parameters pq = (p, q): z > 0: softplus(p) z^2 + z / 2; else (1/2 + softplus(q)) (e^z - 1 - z) + z / 2
-template <typename T>
+template <typename T, int V>
 __global__ void xielu_kernel(const T* __restrict__ z, T* __restrict__ y, long long n, const float* __restrict__ pq) {
-  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * V;
   if (i >= n) return;
   const float p = pq[0], q = pq[1];
   const float ap = p > 20.f ? p : log1pf(expf(p));
   const float aq = 0.5f + (q > 20.f ? q : log1pf(expf(q)));
-  const float v = to_f32<T>(z[i]);
-  const float r = v > 0.f ? ap * v * v + 0.5f * v : aq * (expm1f(v) - v) + 0.5f * v;
-  y[i] = from_f32<T>(r);
+  T in[V], ov[V];
+  if (V > 1) *reinterpret_cast<uint4*>(in) = *reinterpret_cast<const uint4*>(z + i);
+  else in[0] = z[i];
+#pragma unroll
+  for (int j = 0; j < V; ++j) {
+    const float v = to_f32<T>(in[j]);
+    ov[j] = from_f32<T>(v > 0.f ? ap * v * v + 0.5f * v : aq * (expm1f(v) - v) + 0.5f * v);
+  }
+  if (V > 1) *reinterpret_cast<uint4*>(y + i) = *reinterpret_cast<const uint4*>(ov);
+  else y[i] = ov[0];
 }
 
 // out[t, g, :] = o[t, g, :] / sqrt(mean_g(o^2) + eps) * w[:] * sigmoid(gate[t, g, :])   (groups of GS columns; w [GS] shared)
@@ -142,8 +149,11 @@ B200_API int b200_hc_step(const void* y, const float* ls, float* X, const float*
 B200_API int b200_xielu(const void* z, void* y, long long n, const float* pq, int dtype, void* stream) {
   using namespace b200;
   if (n <= 0) return 0;
-  const unsigned grid = (unsigned)((n + 255) / 256);
-  B200_DISPATCH_T(dtype, xielu_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>((const T*)z, (T*)y, n, pq));
+  const int V = dtype == B200_DT_FP32 ? 4 : 8;
+  const bool vec = n % V == 0 && !((reinterpret_cast<uintptr_t>(z) | reinterpret_cast<uintptr_t>(y)) & 15);
+  const unsigned grid = (unsigned)(((vec ? n / V : n) + 255) / 256);
+  if (vec) { B200_DISPATCH_T(dtype, xielu_kernel<T, 16 / sizeof(T)><<<grid, 256, 0, (cudaStream_t)stream>>>((const T*)z, (T*)y, n, pq)); }
+  else { B200_DISPATCH_T(dtype, xielu_kernel<T, 1><<<grid, 256, 0, (cudaStream_t)stream>>>((const T*)z, (T*)y, n, pq)); }
   B200_LAUNCH_CHECK();
   return 0;
 }

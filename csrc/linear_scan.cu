@@ -24,25 +24,35 @@ namespace b200 {
 
 __device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); }
 
+// V channels per thread (V = 4: rows of x, y, the tail and C are multiples of four floats on 16-byte boundaries)
+template <int V>
 __global__ void short_conv_kernel(const float* __restrict__ x, long long ldx, const float* __restrict__ w,
                                   const float* __restrict__ state, const int* __restrict__ pos, const int* __restrict__ slot,
                                   float* __restrict__ y, long long ldy, int tokens, int C, int taps, int act) {
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= (long long)tokens * C) return;
-  const int t = (int)(idx / C), c = (int)(idx % C);
+  const int CV = C / V;
+  if (idx >= (long long)tokens * CV) return;
+  const int t = (int)(idx / CV), c = (int)(idx % CV) * V;
   const int p = pos[t], s = slot[t];
   // nb: tokens of the same run right before t (at most taps - 1 matter)
   int nb = 0;
   while (nb < taps - 1 && t - nb - 1 >= 0 && slot[t - nb - 1] == s) ++nb;
-  float acc = 0.f;
+  float acc[V];
+#pragma unroll
+  for (int e = 0; e < V; ++e) acc[e] = 0.f;
   for (int d = 0; d < taps; ++d) {                       // d tokens back
     if (p - d < 0) break;
-    float v;
-    if (d <= nb) v = x[(long long)(t - d) * ldx + c];
-    else v = state[((long long)s * (taps - 1) + (taps - 1 - (d - nb))) * C + c];
-    acc = fmaf(w[(long long)c * taps + (taps - 1 - d)], v, acc);
+    const float* src = d <= nb ? x + (long long)(t - d) * ldx + c : state + ((long long)s * (taps - 1) + (taps - 1 - (d - nb))) * C + c;
+    float v[V];
+    if (V == 4) *reinterpret_cast<float4*>(v) = *reinterpret_cast<const float4*>(src);
+    else v[0] = src[0];
+#pragma unroll
+    for (int e = 0; e < V; ++e) acc[e] = fmaf(w[(long long)(c + e) * taps + (taps - 1 - d)], v[e], acc[e]);
   }
-  y[(long long)t * ldy + c] = act ? silu_f(acc) : acc;
+#pragma unroll
+  for (int e = 0; e < V; ++e) acc[e] = act ? silu_f(acc[e]) : acc[e];
+  if (V == 4) *reinterpret_cast<float4*>(y + (long long)t * ldy + c) = *reinterpret_cast<const float4*>(acc);
+  else y[(long long)t * ldy + c] = acc[0];
 }
 
 constexpr int kMaxTaps = 16;
@@ -103,15 +113,26 @@ delta_gates_kernel(float* __restrict__ q, long long ldq, float* __restrict__ k, 
 
 constexpr int kScanChunk = 16;
 
-// grid (runs, H, column blocks); block = NW warps; a warp covers 32 / LPC columns, lane = l * (32 / LPC) + jj
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async16f(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// grid (runs, H, column blocks); block = NW warps; a warp covers 32 / LPC columns, lane = l * (32 / LPC) + jj. The chunk of
+// tokens after the one being walked is already on its way into the other shared-memory buffer (cp.async), so the walk
+// waits for global memory once per run, not once per chunk. `vec`: rows of q / k / g start on 16-byte boundaries.
 template <int R, int MODE>
 __global__ void __launch_bounds__(128)
 linear_scan_kernel(const float* __restrict__ q, long long ldq, const float* __restrict__ k, long long ldk,
                    const float* __restrict__ v, long long ldv, const float* __restrict__ g, long long ldg,
                    const float* __restrict__ beta, long long ldb, const float* __restrict__ decay, float* __restrict__ state,
                    const int* __restrict__ runs, const int* __restrict__ pos, const int* __restrict__ slot,
-                   float* __restrict__ o, int H, int G, int D, int Dv, int LPC, int act) {
-  extern __shared__ float sm[];
+                   float* __restrict__ o, int H, int G, int D, int Dv, int LPC, int act, int vec) {
+  extern __shared__ __align__(16) float sm[];
   const int r_ = blockIdx.x, h = blockIdx.y;
   int first, n, p0, s;
   if (runs) { first = runs[4 * r_]; n = runs[4 * r_ + 1]; p0 = runs[4 * r_ + 2]; s = runs[4 * r_ + 3]; }
@@ -126,70 +147,121 @@ linear_scan_kernel(const float* __restrict__ q, long long ldq, const float* __re
   const bool live = j < Dv;
   const int row0 = l * R;
   const int DP = LPC * R;                                 // padded key size
-  float* ks = sm;                                         // [chunk][DP]
-  float* qs = ks + kScanChunk * DP;
-  float* gs = qs + kScanChunk * DP;                       // MODE 1 only
-  float* vs = gs + (MODE == 1 ? kScanChunk * DP : 0);     // [chunk][ncol]
-  float* bs = vs + kScanChunk * ncol;                     // [chunk]
+  const int ncp = (ncol + 3) & ~3;
+  const int per = kScanChunk * DP * (MODE == 1 ? 3 : 2) + kScanChunk * ncp + kScanChunk;      // floats per buffer
+  auto KS = [&](int b) { return sm + b * per; };                                               // [chunk][DP]
+  auto QS = [&](int b) { return sm + b * per + kScanChunk * DP; };
+  auto GS = [&](int b) { return sm + b * per + 2 * kScanChunk * DP; };                         // MODE 1 only
+  auto VS = [&](int b) { return sm + b * per + (MODE == 1 ? 3 : 2) * kScanChunk * DP; };       // [chunk][ncp]
+  auto BS = [&](int b) { return VS(b) + kScanChunk * ncp; };                                   // [chunk]
+  // padding rows (D <= d < DP) never arrive by copy: k = q = 0 (and a finite g) keep their state at zero
+  if (DP > D) {
+    const int padw = DP - D;
+    for (int i = threadIdx.x; i < 2 * kScanChunk * padw; i += blockDim.x) {
+      const int b = i / (kScanChunk * padw), r = i % (kScanChunk * padw);
+      const int at = (r / padw) * DP + D + r % padw;
+      KS(b)[at] = 0.f;
+      QS(b)[at] = 0.f;
+      if (MODE == 1) GS(b)[at] = 0.f;
+    }
+  }
   float S[R];
   float* sp = state + (((long long)s * H + h) * D) * Dv;
 #pragma unroll
   for (int i = 0; i < R; ++i) S[i] = (p0 > 0 && live && row0 + i < D) ? sp[(long long)(row0 + i) * Dv + j] : 0.f;
   const float dec = MODE == 0 ? decay[h] : 0.f;
-  for (int c0 = 0; c0 < n; c0 += kScanChunk) {
+
+  auto stage = [&](int b, int c0) {
     const int cn = min(kScanChunk, n - c0);
-    __syncthreads();
-    for (int i = threadIdx.x; i < cn * DP; i += blockDim.x) {
-      const int tt = i / DP, d = i % DP;
+    for (int tt = warp; tt < cn; tt += nw) {
       const long long tr = first + c0 + tt;
-      float kv = 0.f, qv = 0.f, gv = 1.f;
-      if (d < D) {
-        kv = k[tr * ldk + (long long)kvh * D + d];
-        qv = q[tr * ldq + (long long)kvh * D + d];
-        if (act) { kv = silu_f(kv); qv = silu_f(qv); }
-        if (MODE == 1) gv = g[tr * ldg + (long long)h * D + d];
-      }
-      ks[i] = kv; qs[i] = qv;
-      if (MODE == 1) gs[i] = gv;
-    }
-    for (int i = threadIdx.x; i < cn * ncol; i += blockDim.x) {
-      const int tt = i / ncol, cc = i % ncol;
-      float vv = 0.f;
-      if (col0 + cc < Dv) { vv = v[(long long)(first + c0 + tt) * ldv + (long long)h * Dv + col0 + cc]; if (act) vv = silu_f(vv); }
-      vs[i] = vv;
-    }
-    if (MODE == 1) for (int i = threadIdx.x; i < cn; i += blockDim.x) bs[i] = beta[(long long)(first + c0 + i) * ldb + h];
-    __syncthreads();
-    for (int tt = 0; tt < cn; ++tt) {
-      const float* kr = ks + tt * DP + row0;
-      const float* qr = qs + tt * DP + row0;
-      const float vj = vs[tt * ncol + warp * cpw + jj];
-      float oacc = 0.f;
-      if (MODE == 0) {
-#pragma unroll
-        for (int i = 0; i < R; ++i) {
-          S[i] = fmaf(dec, S[i], kr[i] * vj);
-          oacc = fmaf(S[i], qr[i], oacc);
+      const float* kr = k + tr * ldk + (long long)kvh * D;
+      const float* qr = q + tr * ldq + (long long)kvh * D;
+      const float* gr = MODE == 1 ? g + tr * ldg + (long long)h * D : nullptr;
+      if (vec) {
+        for (int d = lane * 4; d < D; d += 128) {
+          cp_async16f(KS(b) + tt * DP + d, kr + d);
+          cp_async16f(QS(b) + tt * DP + d, qr + d);
+          if (MODE == 1) cp_async16f(GS(b) + tt * DP + d, gr + d);
         }
       } else {
-        const float* gr = gs + tt * DP + row0;
-        float dot = 0.f;
-#pragma unroll
-        for (int i = 0; i < R; ++i) {
-          S[i] *= gr[i];
-          dot = fmaf(S[i], kr[i], dot);
+        for (int d = lane; d < D; d += 32) {
+          cp_async4(KS(b) + tt * DP + d, kr + d);
+          cp_async4(QS(b) + tt * DP + d, qr + d);
+          if (MODE == 1) cp_async4(GS(b) + tt * DP + d, gr + d);
         }
+      }
+      const float* vr = v + tr * ldv + (long long)h * Dv + col0;
+      for (int cc = lane; cc < ncol && col0 + cc < Dv; cc += 32) cp_async4(VS(b) + tt * ncp + cc, vr + cc);
+      if (MODE == 1 && lane == 0) cp_async4(BS(b) + tt, beta + tr * ldb + h);
+    }
+  };
+
+  stage(0, 0);
+  cp_commit();
+  int buf = 0;
+  for (int c0 = 0; c0 < n; c0 += kScanChunk, buf ^= 1) {
+    const int cn = min(kScanChunk, n - c0);
+    const bool more = c0 + kScanChunk < n;
+    if (more) stage(buf ^ 1, c0 + kScanChunk);
+    cp_commit();
+    cp_wait<1>();
+    __syncthreads();
+    if (act) {
+      for (int i = threadIdx.x; i < cn * DP; i += blockDim.x) { KS(buf)[i] = silu_f(KS(buf)[i]); QS(buf)[i] = silu_f(QS(buf)[i]); }
+      for (int i = threadIdx.x; i < cn * ncp; i += blockDim.x) VS(buf)[i] = silu_f(VS(buf)[i]);
+      __syncthreads();
+    }
+    const float* ks = KS(buf);
+    const float* qs = QS(buf);
+    const float* gs = GS(buf);
+    const float* vs = VS(buf);
+    const float* bs = BS(buf);
+    for (int tt = 0; tt < cn; ++tt) {
+      float kr[R], qr[R];
+#pragma unroll
+      for (int i = 0; i < R; i += 4) {
+        *reinterpret_cast<float4*>(kr + i) = *reinterpret_cast<const float4*>(ks + tt * DP + row0 + i);
+        *reinterpret_cast<float4*>(qr + i) = *reinterpret_cast<const float4*>(qs + tt * DP + row0 + i);
+      }
+      const float vj = vs[tt * ncp + warp * cpw + jj];
+      float o0 = 0.f, o1 = 0.f;
+      if (MODE == 0) {
+#pragma unroll
+        for (int i = 0; i < R; i += 2) {
+          S[i] = fmaf(dec, S[i], kr[i] * vj);
+          S[i + 1] = fmaf(dec, S[i + 1], kr[i + 1] * vj);
+          o0 = fmaf(S[i], qr[i], o0);
+          o1 = fmaf(S[i + 1], qr[i + 1], o1);
+        }
+      } else {
+        float gr[R];
+#pragma unroll
+        for (int i = 0; i < R; i += 4) *reinterpret_cast<float4*>(gr + i) = *reinterpret_cast<const float4*>(gs + tt * DP + row0 + i);
+        float d0 = 0.f, d1 = 0.f;
+#pragma unroll
+        for (int i = 0; i < R; i += 2) {
+          S[i] *= gr[i];
+          S[i + 1] *= gr[i + 1];
+          d0 = fmaf(S[i], kr[i], d0);
+          d1 = fmaf(S[i + 1], kr[i + 1], d1);
+        }
+        float dot = d0 + d1;
         for (int x = cpw; x < 32; x <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, x);
         const float u = bs[tt] * (vj - dot);
 #pragma unroll
-        for (int i = 0; i < R; ++i) {
+        for (int i = 0; i < R; i += 2) {
           S[i] = fmaf(kr[i], u, S[i]);
-          oacc = fmaf(S[i], qr[i], oacc);
+          S[i + 1] = fmaf(kr[i + 1], u, S[i + 1]);
+          o0 = fmaf(S[i], qr[i], o0);
+          o1 = fmaf(S[i + 1], qr[i + 1], o1);
         }
       }
+      float oacc = o0 + o1;
       for (int x = cpw; x < 32; x <<= 1) oacc += __shfl_xor_sync(0xffffffffu, oacc, x);
       if (l == 0 && live) o[((long long)(first + c0 + tt) * H + h) * Dv + j] = oacc;
     }
+    __syncthreads();
   }
   if (live) {
 #pragma unroll
@@ -204,8 +276,12 @@ B200_API int b200_short_conv(const float* x, long long ldx, const float* w, cons
   using namespace b200;
   if (tokens <= 0) return 0;
   if (C <= 0 || taps < 1 || taps > kMaxTaps) return B200_ERR_BAD_SHAPE;
-  const long long n = (long long)tokens * C;
-  short_conv_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, ldx, w, state, pos, slot, y, ldy, tokens, C, taps, act);
+  cudaStream_t st = (cudaStream_t)stream;
+  const bool vec = C % 4 == 0 && ldx % 4 == 0 && ldy % 4 == 0 &&
+                   !((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(state)) & 15);
+  const long long n = (long long)tokens * (vec ? C / 4 : C);
+  if (vec) short_conv_kernel<4><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(x, ldx, w, state, pos, slot, y, ldy, tokens, C, taps, act);
+  else short_conv_kernel<1><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(x, ldx, w, state, pos, slot, y, ldy, tokens, C, taps, act);
   B200_LAUNCH_CHECK();
   return 0;
 }
@@ -249,17 +325,26 @@ B200_API int b200_linear_scan(const float* q, long long ldq, const float* k, lon
   const int ncol = nw * cpw;
   const int zb = (Dv + ncol - 1) / ncol;
   const int DP = LPC * R;
-  const size_t smem = ((size_t)kScanChunk * DP * (mode == 1 ? 3 : 2) + (size_t)kScanChunk * ncol + kScanChunk) * 4;
-  if (smem > 48 * 1024) return B200_ERR_TOO_LARGE;
+  const int ncp = (ncol + 3) & ~3;
+  const size_t smem = 2 * ((size_t)kScanChunk * DP * (mode == 1 ? 3 : 2) + (size_t)kScanChunk * ncp + kScanChunk) * 4;
+  if (smem > 200 * 1024) return B200_ERR_TOO_LARGE;
+  auto al = [](const void* p_, long long ld) { return !(reinterpret_cast<uintptr_t>(p_) & 15) && ld % 4 == 0; };
+  const int vec = D % 4 == 0 && al(q, ldq) && al(k, ldk) && (mode == 0 || al(g, ldg));
   dim3 grid(n_runs, H, zb);
   cudaStream_t st = (cudaStream_t)stream;
+#define SCAN_K(RR, MM)                                                                                                     \
+  do {                                                                                                                     \
+    auto kern = linear_scan_kernel<RR, MM>;                                                                                \
+    if (smem > 48 * 1024) B200_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));  \
+    kern<<<grid, nw * 32, smem, st>>>(q, ldq, k, ldk, v, ldv, g, ldg, beta, ldb, decay, state, runs, pos, slot, o, H, G, D, Dv, LPC, act, vec); \
+  } while (0)
 #define SCAN(RR)                                                                                                           \
   do {                                                                                                                     \
-    if (mode == 0) linear_scan_kernel<RR, 0><<<grid, nw * 32, smem, st>>>(q, ldq, k, ldk, v, ldv, g, ldg, beta, ldb, decay, state, runs, pos, slot, o, H, G, D, Dv, LPC, act); \
-    else linear_scan_kernel<RR, 1><<<grid, nw * 32, smem, st>>>(q, ldq, k, ldk, v, ldv, g, ldg, beta, ldb, decay, state, runs, pos, slot, o, H, G, D, Dv, LPC, act); \
+    if (mode == 0) SCAN_K(RR, 0); else SCAN_K(RR, 1);                                                                      \
   } while (0)
   if (R == 8) SCAN(8); else if (R == 16) SCAN(16); else SCAN(32);
 #undef SCAN
+#undef SCAN_K
   B200_LAUNCH_CHECK();
   return 0;
 }

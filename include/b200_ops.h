@@ -552,10 +552,12 @@ int b200_qknorm_rope_store(const float* proj, long long ld, const float* wq, con
                            int has_kv, int dtype, void* stream);
 /* out [tokens, H * Dv]: token t sees key j <= pos[t] of its row if pos[t] - j < window or j < keep_first (window <= 0: all).
  * Each of the M maps is a softmax attention over the same values; combine (M = 2): o = a_0 - lambda a_1, then
- * o / sqrt(mean(o^2) + eps) * post. Dv <= 256. fp32 arithmetic. */
+ * o / sqrt(mean(o^2) + eps) * post. Dv <= 256. fp32 arithmetic. nsplit > 1 cuts every token's visible keys into ranges
+ * (part: fp32 [tokens, H, M, nsplit, Dv + 2] scratch). */
 int b200_multimap_attn(const void* q, const void* ck, const void* cv, const int* pos, const int* slot, const int* table,
-                       int max_blocks, void* out, int tokens, int H, int G, int M, int D, int Dv, int block_size, float scale,
-                       int window, int keep_first, int combine, float lambda, float post, float eps, int dtype, void* stream);
+                       int max_blocks, void* out, float* part, int tokens, int H, int G, int M, int D, int Dv, int block_size,
+                       float scale, int window, int keep_first, int nsplit, int combine, float lambda, float post, float eps,
+                       int dtype, void* stream);
 /* The same for bf16 prompt pieces on mma.sync: tiles int32 [n_tiles, 4] = (first row, rows <= 64, position of the first row,
  * cache row). D in {32, 48, 64, 96, 128}, Dv in {32, 64, 96, 128}, block_size a power of two, scale > 0; else
  * B200_ERR_UNSUPPORTED (use b200_multimap_attn). */

@@ -214,7 +214,7 @@ class DuratarLayer(nn.Module):
         return self._lambda
 
     # ------------------------------------------------------------------ mixers: h [T, W] -> fp32 [T, W]
-    def attention(self, h, cos, sin, pos, slot, cache, src: int, eps: float, pieces):
+    def attention(self, h, cos, sin, pos, slot, cache, src: int, eps: float, pieces, max_pos: int = 0):
         m = self.spec.mixer
         H, G, D, Dv = m.heads, m.kv_heads, m.dim, m.vdim
         own = m.kv_from is None
@@ -223,7 +223,8 @@ class DuratarLayer(nn.Module):
                               cache.k[self.idx] if own else None, cache.v[self.idx] if own else None, cache.table,
                               H, G, MAPS, D, Dv, m.rot_dims, eps, h.dtype)
         ctx = multimap_attention(q, cache.k[src], cache.v[src], cache.table, pos, slot, H, G, MAPS, D, Dv, m.scale, m.window,
-                                 m.keep_first, combine=True, lam=self.diff_lambda(), post=1.0 - m.diff, eps=eps, pieces=pieces)
+                                 m.keep_first, combine=True, lam=self.diff_lambda(), post=1.0 - m.diff, eps=eps, pieces=pieces,
+                                 max_pos=max_pos)
         return linear_exact(ctx, self.o_proj, out_dtype=torch.float32)
 
     def lightning(self, h, pos, slot, cache, runs, n_runs, eps: float):
@@ -348,7 +349,7 @@ class DuratarForCausalLM(nn.Module):
                     cos, sin = self.rope(li, dev, need)
                 else:
                     cos = sin = torch.zeros(1, 1, dtype=torch.float32, device=dev)
-                y = layer.attention(h, cos, sin, pos, slot, cache, li if m.kv_from is None else m.kv_from, eps, pieces)
+                y = layer.attention(h, cos, sin, pos, slot, cache, li if m.kv_from is None else m.kv_from, eps, pieces, max_pos)
             elif m.kind == "lightning":
                 y = layer.lightning(h, pos, slot, cache, runs, n_runs, eps)
             else:

@@ -24,6 +24,7 @@ from . import _native as nv
 
 vp, i32, i64, f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
 _MMA_D, _MMA_DV = (32, 48, 64, 96, 128), (32, 64, 96, 128)        # sizes the tensor-core kernel is built for
+_SPLIT_KEYS = int(os.environ.get("B200_PAGED_SPLIT_KEYS", "512"))  # keys per range of a small batch with many visible keys
 
 
 def qknorm_rope_store(proj: torch.Tensor, wq: torch.Tensor, wk: Optional[torch.Tensor], cos: torch.Tensor, sin: torch.Tensor,
@@ -74,10 +75,11 @@ def qknorm_rope_store(proj: torch.Tensor, wq: torch.Tensor, wk: Optional[torch.T
 def multimap_attention(q: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tensor, table: torch.Tensor, pos: torch.Tensor,
                        slot: torch.Tensor, H: int, G: int, M: int, D: int, Dv: int, scale: float, window: int = 0,
                        keep_first: int = 0, combine: bool = False, lam: float = 0.0, post: float = 1.0, eps: float = 0.0,
-                       pieces=None) -> torch.Tensor:
+                       pieces=None, max_pos: int = 0) -> torch.Tensor:
     """Context [T, H * Dv] (q's dtype) of ``q`` [T, H * M * D] over the pools; see the module docstring for the mask and the
     combination. ``pieces`` (``inference.ragged.Pieces``): bf16 steps with a run of 8 or more tokens go through the tensor-core
-    kernel; everything else (fp32, decode batches, sizes it is not built for) through the per-(token, head) kernel."""
+    kernel; everything else (fp32, decode batches, sizes it is not built for) through the per-token kernels. ``max_pos``: an upper
+    bound of ``pos`` known on the host (0 = unknown), used to cut the keys of a small batch into ranges."""
     T = q.shape[0]
     BS = cache_k.shape[2]
     out = torch.empty(T, H * Dv, dtype=q.dtype, device=q.device)
@@ -93,12 +95,20 @@ def multimap_attention(q: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Te
                         float(lam), float(post), float(eps), nv.dtype_code(q.dtype), nv.stream()), "multimap_attn_mma")
             nv.count_launch()
             return out
-        fn = nv.proto("b200_multimap_attn", [vp, vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, i32, f32, i32, i32, i32,
-                                             f32, f32, f32, i32, vp])
+        # few tokens with many visible keys (a small decode batch with a wide window or none): cut the keys into ranges
+        seen = max_pos + 1 if max_pos > 0 else 0
+        if window > 0:
+            seen = min(seen, window + max(keep_first, 0))
+        nsplit = 1
+        if seen > 2 * _SPLIT_KEYS and T * G < 296:
+            nsplit = min(32, -(-seen // _SPLIT_KEYS), max(1, 592 // (T * G)))
+        part = torch.empty(T * H * M * nsplit * (Dv + 2), dtype=torch.float32, device=q.device) if nsplit > 1 else None
+        fn = nv.proto("b200_multimap_attn", [vp, vp, vp, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, i32, f32, i32, i32,
+                                             i32, i32, f32, f32, f32, i32, vp])
         nv.check(fn(nv.ptr(q), nv.ptr(cache_k), nv.ptr(cache_v), nv.ptr(pos), nv.ptr(slot), nv.ptr(table), table.shape[1],
-                    nv.ptr(out), T, H, G, M, D, Dv, BS, float(scale), int(window), int(keep_first), int(combine), float(lam),
-                    float(post), float(eps), nv.dtype_code(q.dtype), nv.stream()), "multimap_attn")
-        nv.count_launch()
+                    nv.ptr(out), nv.ptr(part), T, H, G, M, D, Dv, BS, float(scale), int(window), int(keep_first), nsplit, int(combine),
+                    float(lam), float(post), float(eps), nv.dtype_code(q.dtype), nv.stream()), "multimap_attn")
+        nv.count_launch(2 if nsplit > 1 else 1)
         return out
     rep = H // G
     pl, sl = pos.tolist(), slot.tolist()

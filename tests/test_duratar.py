@@ -217,7 +217,7 @@ def test_qknorm_rope_store(device, dtype, H, G, D, Dv, rot, own):
             torch.testing.assert_close(cv[blk, :, p % BS].cpu().double(), proj[i, nq + nk:nq + nk + G * Dv].double().view(G, Dv), rtol=t, atol=t)
 
 
-def _attention_case(device, dtype, H, G, D, Dv, size, keep, n, seed, targets, as_piece):
+def _attention_case(device, dtype, H, G, D, Dv, size, keep, n, seed, targets, as_piece, max_pos=0):
     """Random q / k / v of one sequence with, for each (query position, key position) in ``targets``, the key scaled so that
     its score dominates if it is seen; the values of target keys are large, so a wrong mask moves the output by its size."""
     from llm_in_practise_b200.inference.ragged import Pieces
@@ -252,7 +252,7 @@ def _attention_case(device, dtype, H, G, D, Dv, size, keep, n, seed, targets, as
         sel, pieces = rows, None
     pos = torch.tensor(sel, dtype=torch.int32, device=device)
     out = multimap_attention(q[sel].reshape(len(sel), -1).to(device), ck, cv, table, pos, torch.ones_like(pos), H, G, 2, D, Dv, scale,
-                             size, keep, combine=True, lam=lam, post=1 - diff, eps=eps, pieces=pieces)
+                             size, keep, combine=True, lam=lam, post=1 - diff, eps=eps, pieces=pieces, max_pos=max_pos)
     got = out.view(len(sel), H, Dv)
     for i, p in enumerate(sel):
         assert rel_err(got[i], ref[p]) < tol(dtype), (p, as_piece)
@@ -275,6 +275,16 @@ def test_attention_window_edges_and_far_keys(device, dtype, as_piece, H, G, D, D
     _attention_case(device, dtype, H, G, D, Dv, 0, 0, n, 6, [(329, 20), (328, 0), (300, 299)], as_piece)
     # the window covers less than the kept tokens near the start of a sequence
     _attention_case(device, dtype, H, G, D, Dv, 3, 10, 40, 7, [(12, 9), (12, 10), (12, 8), (2, 0), (11, 2), (39, 9), (39, 36), (38, 35)], as_piece)
+
+
+@pytest.mark.parametrize("device,dtype", CASES)
+@pytest.mark.parametrize("H,G,D,Dv,size,keep", [(4, 2, 32, 64, 0, 0), (2, 1, 24, 40, 0, 0), (4, 1, 64, 128, 1200, 30)])
+def test_attention_long_context_decode_in_key_ranges(device, dtype, H, G, D, Dv, size, keep):
+    """Few single tokens far into a sequence: their visible keys are cut into ranges that are merged afterwards; dominant
+    keys sit in the first, a middle and the last range, at range borders and (with a window) on both sides of its edge."""
+    n = 1400
+    targets = [(1399, 0), (1398, 511), (1397, 512), (1396, 1396), (1395, 700), (1394, 1394 - 1199), (1393, 1393 - 1200), (1392, 29), (1391, 30)]
+    _attention_case(device, dtype, H, G, D, Dv, size, keep, n, 9, targets, False, max_pos=n - 1)
 
 
 @pytest.mark.parametrize("device,dtype", [("cpu", torch.float32), pytest.param("cuda", torch.float32, marks=pytest.mark.gpu)])
