@@ -203,7 +203,7 @@ def kernel_rows(size, dev, steps, warmup, root):
     state = torch.zeros(65, SH, SD, SDv, device=dev)
     dec = torch.full((SH,), 0.99, device=dev)
     q16, k16 = torch.randn(T, SH * SD, device=dev) * SD ** -0.5, torch.randn(T, SH * SD, device=dev) * SD ** -0.5
-    for mode, fl_tok, args in (("decay", 2 * 2 * SD * SDv, dict(decay=dec, act=True)), ("delta", 3 * 2 * SD * SDv, dict(g=ga, beta=be))):
+    for mode, fl_tok, args in (("decay", 2 * 2 * SD * SDv, dict(decay=dec)), ("delta", 3 * 2 * SD * SDv, dict(g=ga, beta=be))):
         qq, kk, g_ = (q16, k16, SH) if mode == "decay" else (qs, ks, SG)
         ms_d = t(lambda: linear_scan(qq, kk, vs, state, pos, slot, runs, 1, SH, g_, SD, SDv, mode, **args), steps, warmup)
         fr = SH * fl_tok * T / (ms_d * 1e-3) / 1e12 / FP32_TFLOPS

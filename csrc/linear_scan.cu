@@ -8,6 +8,8 @@
 //
 //   b200_short_conv        y[t, c] = act(sum_j w[c, j] x[t - (taps - 1) + j, c]); inputs before the run come from the tail
 //                          kept in `state` [rows, taps - 1, C] (the last taps - 1 inputs; zeros before position 0).
+//   b200_silu_rows         x <- silu(x) in place on a column slice of fp32 rows (the activation of projections that enter a
+//                          scan without a convolution, done once instead of by every CTA that reads them).
 //   b200_short_conv_tail   advances that tail over the step's runs (launched after the convolution has read the old one).
 //   b200_delta_gates       q, k -> unit vectors per head (q also times `qscale`); a -> exp(-exp(A_log[h]) softplus(a + bias));
 //                          b -> sigmoid(b); in place, fp32.
@@ -56,6 +58,22 @@ __global__ void short_conv_kernel(const float* __restrict__ x, long long ldx, co
 }
 
 constexpr int kMaxTaps = 16;
+
+// x[r, c] <- silu(x[r, c]) over the first `cols` columns of rows of stride ld
+template <int V>
+__global__ void silu_rows_kernel(float* __restrict__ x, long long ld, long long rows, int cols) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int CV = cols / V;
+  if (idx >= rows * CV) return;
+  float* px = x + (idx / CV) * ld + (idx % CV) * V;
+  float v[V];
+  if (V == 4) *reinterpret_cast<float4*>(v) = *reinterpret_cast<const float4*>(px);
+  else v[0] = px[0];
+#pragma unroll
+  for (int e = 0; e < V; ++e) v[e] = silu_f(v[e]);
+  if (V == 4) *reinterpret_cast<float4*>(px) = *reinterpret_cast<const float4*>(v);
+  else px[0] = v[0];
+}
 
 __global__ void short_conv_tail_kernel(const float* __restrict__ x, long long ldx, float* __restrict__ state,
                                        const int* __restrict__ runs, const int* __restrict__ pos, const int* __restrict__ slot,
@@ -146,7 +164,9 @@ linear_scan_kernel(const float* __restrict__ q, long long ldq, const float* __re
   const int j = col0 + warp * cpw + jj;
   const bool live = j < Dv;
   const int row0 = l * R;
-  const int DP = LPC * R;                                 // padded key size
+  constexpr int RP = R + 4;                               // a lane group's rows, padded so that the groups' 16-byte reads
+  const int DP = LPC * RP;                                // of one token fall into different banks
+  auto at = [](int d) { return (d / R) * RP + d % R; };   // key channel d -> its place in a staged row
   const int ncp = (ncol + 3) & ~3;
   const int per = kScanChunk * DP * (MODE == 1 ? 3 : 2) + kScanChunk * ncp + kScanChunk;      // floats per buffer
   auto KS = [&](int b) { return sm + b * per; };                                               // [chunk][DP]
@@ -155,14 +175,14 @@ linear_scan_kernel(const float* __restrict__ q, long long ldq, const float* __re
   auto VS = [&](int b) { return sm + b * per + (MODE == 1 ? 3 : 2) * kScanChunk * DP; };       // [chunk][ncp]
   auto BS = [&](int b) { return VS(b) + kScanChunk * ncp; };                                   // [chunk]
   // padding rows (D <= d < DP) never arrive by copy: k = q = 0 (and a finite g) keep their state at zero
-  if (DP > D) {
-    const int padw = DP - D;
+  if (LPC * R > D) {
+    const int padw = LPC * R - D;
     for (int i = threadIdx.x; i < 2 * kScanChunk * padw; i += blockDim.x) {
       const int b = i / (kScanChunk * padw), r = i % (kScanChunk * padw);
-      const int at = (r / padw) * DP + D + r % padw;
-      KS(b)[at] = 0.f;
-      QS(b)[at] = 0.f;
-      if (MODE == 1) GS(b)[at] = 0.f;
+      const int x = (r / padw) * DP + at(D + r % padw);
+      KS(b)[x] = 0.f;
+      QS(b)[x] = 0.f;
+      if (MODE == 1) GS(b)[x] = 0.f;
     }
   }
   float S[R];
@@ -180,15 +200,15 @@ linear_scan_kernel(const float* __restrict__ q, long long ldq, const float* __re
       const float* gr = MODE == 1 ? g + tr * ldg + (long long)h * D : nullptr;
       if (vec) {
         for (int d = lane * 4; d < D; d += 128) {
-          cp_async16f(KS(b) + tt * DP + d, kr + d);
-          cp_async16f(QS(b) + tt * DP + d, qr + d);
-          if (MODE == 1) cp_async16f(GS(b) + tt * DP + d, gr + d);
+          cp_async16f(KS(b) + tt * DP + at(d), kr + d);
+          cp_async16f(QS(b) + tt * DP + at(d), qr + d);
+          if (MODE == 1) cp_async16f(GS(b) + tt * DP + at(d), gr + d);
         }
       } else {
         for (int d = lane; d < D; d += 32) {
-          cp_async4(KS(b) + tt * DP + d, kr + d);
-          cp_async4(QS(b) + tt * DP + d, qr + d);
-          if (MODE == 1) cp_async4(GS(b) + tt * DP + d, gr + d);
+          cp_async4(KS(b) + tt * DP + at(d), kr + d);
+          cp_async4(QS(b) + tt * DP + at(d), qr + d);
+          if (MODE == 1) cp_async4(GS(b) + tt * DP + at(d), gr + d);
         }
       }
       const float* vr = v + tr * ldv + (long long)h * Dv + col0;
@@ -217,12 +237,13 @@ linear_scan_kernel(const float* __restrict__ q, long long ldq, const float* __re
     const float* gs = GS(buf);
     const float* vs = VS(buf);
     const float* bs = BS(buf);
+#pragma unroll 2
     for (int tt = 0; tt < cn; ++tt) {
       float kr[R], qr[R];
 #pragma unroll
       for (int i = 0; i < R; i += 4) {
-        *reinterpret_cast<float4*>(kr + i) = *reinterpret_cast<const float4*>(ks + tt * DP + row0 + i);
-        *reinterpret_cast<float4*>(qr + i) = *reinterpret_cast<const float4*>(qs + tt * DP + row0 + i);
+        *reinterpret_cast<float4*>(kr + i) = *reinterpret_cast<const float4*>(ks + tt * DP + l * RP + i);
+        *reinterpret_cast<float4*>(qr + i) = *reinterpret_cast<const float4*>(qs + tt * DP + l * RP + i);
       }
       const float vj = vs[tt * ncp + warp * cpw + jj];
       float o0 = 0.f, o1 = 0.f;
@@ -237,7 +258,7 @@ linear_scan_kernel(const float* __restrict__ q, long long ldq, const float* __re
       } else {
         float gr[R];
 #pragma unroll
-        for (int i = 0; i < R; i += 4) *reinterpret_cast<float4*>(gr + i) = *reinterpret_cast<const float4*>(gs + tt * DP + row0 + i);
+        for (int i = 0; i < R; i += 4) *reinterpret_cast<float4*>(gr + i) = *reinterpret_cast<const float4*>(gs + tt * DP + l * RP + i);
         float d0 = 0.f, d1 = 0.f;
 #pragma unroll
         for (int i = 0; i < R; i += 2) {
@@ -286,6 +307,17 @@ B200_API int b200_short_conv(const float* x, long long ldx, const float* w, cons
   return 0;
 }
 
+B200_API int b200_silu_rows(float* x, long long ld, long long rows, int cols, void* stream) {
+  using namespace b200;
+  if (rows <= 0 || cols <= 0) return 0;
+  const bool vec = cols % 4 == 0 && ld % 4 == 0 && !(reinterpret_cast<uintptr_t>(x) & 15);
+  const long long n = rows * (vec ? cols / 4 : cols);
+  if (vec) silu_rows_kernel<4><<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, ld, rows, cols);
+  else silu_rows_kernel<1><<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, ld, rows, cols);
+  B200_LAUNCH_CHECK();
+  return 0;
+}
+
 B200_API int b200_short_conv_tail(const float* x, long long ldx, float* state, const int* runs, const int* pos, const int* slot,
                                   int n_runs, int C, int taps, void* stream) {
   using namespace b200;
@@ -324,7 +356,7 @@ B200_API int b200_linear_scan(const float* q, long long ldq, const float* k, lon
   while (nw > 1 && (nw - 1) * cpw >= Dv) --nw;            // no warp without columns
   const int ncol = nw * cpw;
   const int zb = (Dv + ncol - 1) / ncol;
-  const int DP = LPC * R;
+  const int DP = LPC * (R + 4);
   const int ncp = (ncol + 3) & ~3;
   const size_t smem = 2 * ((size_t)kScanChunk * DP * (mode == 1 ? 3 : 2) + (size_t)kScanChunk * ncp + kScanChunk) * 4;
   if (smem > 200 * 1024) return B200_ERR_TOO_LARGE;

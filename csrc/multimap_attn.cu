@@ -192,26 +192,27 @@ multimap_attn_kernel(const T* __restrict__ q, const T* __restrict__ ck, const T*
   }
 }
 // Vector variant (D and Dv whole 16-byte chunks, at most 32 chunks each): a CTA owns one token, up to HB query heads of one
-// KV group and one range of the visible keys. A lane is (key sub-index, chunk): the CP lanes of a group read the M key rows
-// and the value row of one key with one 16-byte load each; scores are reduced over the group's lanes and every lane keeps
-// its own running (max, sum, acc) per (head, map) — nothing crosses groups inside the loop. Groups are merged by shuffles
-// at the end, the four warps through shared memory; then a warp per head forms the combination and the norm. `nsplit` > 1
-// writes (max, sum, acc) per (token, head, map, split) to `part` for multimap_attn_merge_kernel.
-template <typename T, int HB, int M>
+// KV group, ONE map and one range of the visible keys (blockIdx.z = range * M + map). A lane is (key sub-index, chunk): the
+// CP lanes of a group read the key row of the map and the value row of one key with one 16-byte load each; scores are
+// reduced over the group's lanes and every lane keeps its own running (max, sum, acc) per head — nothing crosses groups
+// inside the loop. Groups are merged by shuffles at the end, the four warps through shared memory. With one map and one
+// range the result is written directly; otherwise (max, sum, acc) go to `part` [tokens, H, M, nsplit, Dv + 2] and
+// multimap_attn_merge_kernel merges ranges and maps.
+template <typename T, int HB>
 __global__ void __launch_bounds__(128)
 multimap_attn_vec_kernel(const T* __restrict__ q, const T* __restrict__ ck, const T* __restrict__ cv, const int* __restrict__ pos,
                          const int* __restrict__ slot, const int* __restrict__ table, int max_blocks, T* __restrict__ out,
-                         float* __restrict__ part, int H, int G, int D, int Dv, int bs_log2, float scale, int window,
-                         int keep_first, int nsplit, int CP, int CPK, int CPV, int combine, float lambda, float post, float eps) {
+                         float* __restrict__ part, int H, int G, int M, int D, int Dv, int bs_log2, float scale, int window,
+                         int keep_first, int nsplit, int CP, int CPK, int CPV) {
   constexpr int E = 16 / sizeof(T);
-  extern __shared__ float sm[];                          // [4 warps][HB][M][Dv + 2]
+  extern __shared__ float sm[];                          // [4 warps][HB][Dv + 2]
   const int t = blockIdx.x;
   const int rep = H / G;
   const int passes = (rep + HB - 1) / HB;
   const int g = blockIdx.y / passes;
   const int h0 = g * rep + (blockIdx.y % passes) * HB;
   const int nh = min(HB, g * rep + rep - h0);
-  const int split = blockIdx.z;
+  const int split = blockIdx.z / M, m = blockIdx.z % M;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int KPI = 32 / CP;
   const int kk = lane / CP, c = lane % CP;
@@ -228,160 +229,112 @@ multimap_attn_vec_kernel(const T* __restrict__ q, const T* __restrict__ ck, cons
     i_lo = split * chunk;
     i_hi = min(total, i_lo + chunk);
   }
-  float qv[HB][M][E], acc[HB][M][E], mx[HB][M], l[HB][M];
+  float qv[HB][E], acc[HB][E], mx[HB], l[HB];
 #pragma unroll
-  for (int hh = 0; hh < HB; ++hh)
+  for (int hh = 0; hh < HB; ++hh) {
+    mx[hh] = -INFINITY;
+    l[hh] = 0.f;
 #pragma unroll
-    for (int m = 0; m < M; ++m) {
-      mx[hh][m] = -INFINITY;
-      l[hh][m] = 0.f;
-#pragma unroll
-      for (int e = 0; e < E; ++e) {
-        acc[hh][m][e] = 0.f;
-        qv[hh][m][e] = (liveK && hh < nh) ? to_f32<T>(q[(((long long)t * H + h0 + hh) * M + m) * D + c * E + e]) * scale : 0.f;
-      }
+    for (int e = 0; e < E; ++e) {
+      acc[hh][e] = 0.f;
+      qv[hh][e] = (liveK && hh < nh) ? to_f32<T>(q[(((long long)t * H + h0 + hh) * M + m) * D + c * E + e]) * scale : 0.f;
     }
+  }
   const int bs_mask = (1 << bs_log2) - 1;
   const int stride = 4 * KPI;
-  constexpr int U = HB * M >= 4 ? 2 : 4;
+  constexpr int U = HB >= 4 ? 2 : 4;
   for (int ib = i_lo; ib < i_hi; ib += stride * U) {
-    uint4 kr[U][M], vr[U];
+    uint4 kr[U], vr[U];
     bool valid[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int i = ib + u * stride + warp * KPI + kk;
       valid[u] = i < i_hi;
-      vr[u] = make_uint4(0, 0, 0, 0);
-#pragma unroll
-      for (int m = 0; m < M; ++m) kr[u][m] = make_uint4(0, 0, 0, 0);
+      kr[u] = vr[u] = make_uint4(0, 0, 0, 0);
       if (valid[u]) {
         const int kp = i < n1 ? i : lo + (i - n1);
         const long long blk = trow[kp >> bs_log2];
         const int off = kp & bs_mask;
-        if (liveK) {
-#pragma unroll
-          for (int m = 0; m < M; ++m)
-            kr[u][m] = *reinterpret_cast<const uint4*>(ck + ((((blk * G + g) * M + m) << bs_log2) + off) * D + c * E);
-        }
+        if (liveK) kr[u] = *reinterpret_cast<const uint4*>(ck + ((((blk * G + g) * M + m) << bs_log2) + off) * D + c * E);
         if (liveV) vr[u] = *reinterpret_cast<const uint4*>(cv + ((((blk * G) + g) << bs_log2) + off) * Dv + c * E);
       }
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       if (ib + u * stride >= i_hi) break;               // uniform over the CTA
-      float vf[E];
+      float kf[E], vf[E];
+      const T* kp_ = reinterpret_cast<const T*>(&kr[u]);
       const T* vp = reinterpret_cast<const T*>(&vr[u]);
 #pragma unroll
-      for (int e = 0; e < E; ++e) vf[e] = to_f32<T>(vp[e]);
+      for (int e = 0; e < E; ++e) { kf[e] = to_f32<T>(kp_[e]); vf[e] = to_f32<T>(vp[e]); }
 #pragma unroll
-      for (int m = 0; m < M; ++m) {
-        float kf[E];
-        const T* kp_ = reinterpret_cast<const T*>(&kr[u][m]);
+      for (int hh = 0; hh < HB; ++hh) {
+        float s = 0.f;
 #pragma unroll
-        for (int e = 0; e < E; ++e) kf[e] = to_f32<T>(kp_[e]);
+        for (int e = 0; e < E; ++e) s = fmaf(qv[hh][e], kf[e], s);
+        for (int o = CP >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if (valid[u]) {
+          const float mn = fmaxf(mx[hh], s);
+          const float r = expf(mx[hh] - mn);            // 0 on the first key (max = -inf)
+          const float pj = expf(s - mn);
+          mx[hh] = mn;
+          l[hh] = l[hh] * r + pj;
 #pragma unroll
-        for (int hh = 0; hh < HB; ++hh) {
-          float s = 0.f;
-#pragma unroll
-          for (int e = 0; e < E; ++e) s = fmaf(qv[hh][m][e], kf[e], s);
-          for (int o = CP >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-          if (valid[u]) {
-            const float mn = fmaxf(mx[hh][m], s);
-            const float r = expf(mx[hh][m] - mn);       // 0 on the first key (max = -inf)
-            const float pj = expf(s - mn);
-            mx[hh][m] = mn;
-            l[hh][m] = l[hh][m] * r + pj;
-#pragma unroll
-            for (int e = 0; e < E; ++e) acc[hh][m][e] = fmaf(pj, vf[e], acc[hh][m][e] * r);
-          }
+          for (int e = 0; e < E; ++e) acc[hh][e] = fmaf(pj, vf[e], acc[hh][e] * r);
         }
       }
     }
   }
   const int LDW = Dv + 2;
 #pragma unroll
-  for (int hh = 0; hh < HB; ++hh)
+  for (int hh = 0; hh < HB; ++hh) {
+    for (int o = CP; o < 32; o <<= 1) {
+      const float m2 = __shfl_xor_sync(0xffffffffu, mx[hh], o);
+      const float l2 = __shfl_xor_sync(0xffffffffu, l[hh], o);
+      const float mn = fmaxf(mx[hh], m2);
+      const float e1 = mx[hh] == -INFINITY ? 0.f : expf(mx[hh] - mn);
+      const float e2 = m2 == -INFINITY ? 0.f : expf(m2 - mn);
+      l[hh] = l[hh] * e1 + l2 * e2;
 #pragma unroll
-    for (int m = 0; m < M; ++m) {
-      for (int o = CP; o < 32; o <<= 1) {
-        const float m2 = __shfl_xor_sync(0xffffffffu, mx[hh][m], o);
-        const float l2 = __shfl_xor_sync(0xffffffffu, l[hh][m], o);
-        const float mn = fmaxf(mx[hh][m], m2);
-        const float e1 = mx[hh][m] == -INFINITY ? 0.f : expf(mx[hh][m] - mn);
-        const float e2 = m2 == -INFINITY ? 0.f : expf(m2 - mn);
-        l[hh][m] = l[hh][m] * e1 + l2 * e2;
-#pragma unroll
-        for (int e = 0; e < E; ++e) {
-          const float a2 = __shfl_xor_sync(0xffffffffu, acc[hh][m][e], o);
-          acc[hh][m][e] = acc[hh][m][e] * e1 + a2 * e2;
-        }
-        mx[hh][m] = mn;
+      for (int e = 0; e < E; ++e) {
+        const float a2 = __shfl_xor_sync(0xffffffffu, acc[hh][e], o);
+        acc[hh][e] = acc[hh][e] * e1 + a2 * e2;
       }
-      if (kk == 0) {
-        float* w = sm + ((warp * HB + hh) * M + m) * LDW;
-        if (c == 0) { w[0] = mx[hh][m]; w[1] = l[hh][m]; }
-        if (liveV) {
+      mx[hh] = mn;
+    }
+    if (kk == 0) {
+      float* w = sm + (warp * HB + hh) * LDW;
+      if (c == 0) { w[0] = mx[hh]; w[1] = l[hh]; }
+      if (liveV) {
 #pragma unroll
-          for (int e = 0; e < E; ++e) w[2 + c * E + e] = acc[hh][m][e];
-        }
+        for (int e = 0; e < E; ++e) w[2 + c * E + e] = acc[hh][e];
       }
     }
+  }
   __syncthreads();
-  // a warp per head: merge the four warps' partial results, then either the final combination or the split record
-  for (int hh = warp; hh < nh; hh += 4) {
+  const bool direct = M == 1 && nsplit == 1;
+  for (int i = threadIdx.x; i < nh * Dv; i += blockDim.x) {
+    const int hh = i / Dv, d = i % Dv;
     const int h = h0 + hh;
-    float res[kAcc];
+    float mt = -INFINITY;
 #pragma unroll
-    for (int a = 0; a < kAcc; ++a) res[a] = 0.f;
-    for (int m = 0; m < M; ++m) {
-      float mt = -INFINITY;
+    for (int w = 0; w < 4; ++w) mt = fmaxf(mt, sm[(w * HB + hh) * LDW]);
+    float lt = 0.f, at = 0.f;
 #pragma unroll
-      for (int w = 0; w < 4; ++w) mt = fmaxf(mt, sm[((w * HB + hh) * M + m) * LDW]);
-      float lt = 0.f, at[kAcc];
-#pragma unroll
-      for (int a = 0; a < kAcc; ++a) at[a] = 0.f;
-#pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        const float* ws = sm + ((w * HB + hh) * M + m) * LDW;
-        if (ws[0] != -INFINITY) {
-          const float e = expf(ws[0] - mt);
-          lt += ws[1] * e;
-#pragma unroll
-          for (int a = 0; a < kAcc; ++a) {
-            const int d = lane + 32 * a;
-            if (d < Dv) at[a] += ws[2 + d] * e;
-          }
-        }
-      }
-      if (nsplit > 1) {
-        float* pr = part + ((((long long)t * H + h) * M + m) * nsplit + split) * LDW;
-        if (lane == 0) { pr[0] = mt; pr[1] = lt; }
-#pragma unroll
-        for (int a = 0; a < kAcc; ++a) {
-          const int d = lane + 32 * a;
-          if (d < Dv) pr[2 + d] = at[a];
-        }
-      } else {
-        const float inv = lt > 0.f ? 1.f / lt : 0.f;
-        const float coef = m == 0 ? 1.f : -lambda;
-#pragma unroll
-        for (int a = 0; a < kAcc; ++a) res[a] = fmaf(coef, at[a] * inv, res[a]);
+    for (int w = 0; w < 4; ++w) {
+      const float* ws = sm + (w * HB + hh) * LDW;
+      if (ws[0] != -INFINITY) {
+        const float e = expf(ws[0] - mt);
+        lt += ws[1] * e;
+        at += ws[2 + d] * e;
       }
     }
-    if (nsplit > 1) continue;
-    float mult = 1.f;
-    if (combine) {
-      float ss = 0.f;
-#pragma unroll
-      for (int a = 0; a < kAcc; ++a) ss += (lane + 32 * a < Dv) ? res[a] * res[a] : 0.f;
-      ss = warp_sum(ss);
-      mult = rsqrtf(ss / Dv + eps) * post;
-    }
-    T* orow = out + ((long long)t * H + h) * Dv;
-#pragma unroll
-    for (int a = 0; a < kAcc; ++a) {
-      const int d = lane + 32 * a;
-      if (d < Dv) orow[d] = from_f32<T>(res[a] * mult);
+    if (direct) {
+      out[((long long)t * H + h) * Dv + d] = from_f32<T>(lt > 0.f ? at / lt : 0.f);
+    } else {
+      float* pr = part + ((((long long)t * H + h) * M + m) * nsplit + split) * LDW;
+      if (d == 0) { pr[0] = mt; pr[1] = lt; }
+      pr[2 + d] = at;
     }
   }
 }
@@ -470,22 +423,24 @@ B200_API int b200_multimap_attn(const void* q, const void* ck, const void* cv, c
     const int CPK = D / E, CPV = Dv / E;
     int bs_log2 = 0;
     while ((1 << bs_log2) < block_size) ++bs_log2;
-    if (D % E == 0 && Dv % E == 0 && CPK <= 32 && CPV <= 32 && (1 << bs_log2) == block_size && (nsplit == 1 || part) &&
+    if (D % E == 0 && Dv % E == 0 && CPK <= 32 && CPV <= 32 && (1 << bs_log2) == block_size && (part || (M == 1 && nsplit == 1)) &&
         !((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(ck) | reinterpret_cast<uintptr_t>(cv)) & 15)) {
       int CP = 1;
       while (CP < CPK || CP < CPV) CP <<= 1;
-      const int HB = rep >= 2 ? 2 : 1;
+      const int HB = rep >= 4 ? 4 : (rep >= 2 ? 2 : 1);
       const int passes = (rep + HB - 1) / HB;
-      if ((long long)G * passes > 65535 || nsplit > 65535) return B200_ERR_TOO_LARGE;
-      dim3 grid(tokens, G * passes, nsplit);
-      const size_t smem = (size_t)4 * HB * M * (Dv + 2) * sizeof(float);
-#define MMV(T, HBV, MV)                                                                                                      \
-  multimap_attn_vec_kernel<T, HBV, MV><<<grid, 128, smem, st>>>((const T*)q, (const T*)ck, (const T*)cv, pos, slot, table,    \
-      max_blocks, (T*)out, part, H, G, D, Dv, bs_log2, scale, window, keep_first, nsplit, CP, CPK, CPV, combine, lambda, post, eps)
+      const bool direct = M == 1 && nsplit == 1;
+      if ((long long)G * passes > 65535 || nsplit * M > 65535) return B200_ERR_TOO_LARGE;
+      if (!direct && !part) return B200_ERR_BAD_SHAPE;
+      dim3 grid(tokens, G * passes, nsplit * M);
+      const size_t smem = (size_t)4 * HB * (Dv + 2) * sizeof(float);
+#define MMV(T, HBV)                                                                                                          \
+  multimap_attn_vec_kernel<T, HBV><<<grid, 128, smem, st>>>((const T*)q, (const T*)ck, (const T*)cv, pos, slot, table,        \
+      max_blocks, (T*)out, part, H, G, M, D, Dv, bs_log2, scale, window, keep_first, nsplit, CP, CPK, CPV)
 #define MMV_T(T)                                                                                                             \
   do {                                                                                                                       \
-    if (HB == 2 && M == 2) MMV(T, 2, 2); else if (HB == 2) MMV(T, 2, 1); else if (M == 2) MMV(T, 1, 2); else MMV(T, 1, 1);  \
-    if (nsplit > 1)                                                                                                          \
+    if (HB == 4) MMV(T, 4); else if (HB == 2) MMV(T, 2); else MMV(T, 1);                                                     \
+    if (!direct)                                                                                                             \
       multimap_attn_merge_kernel<T><<<(unsigned)(((long long)tokens * H + 3) / 4), 128, 0, st>>>(                             \
           part, (T*)out, (long long)tokens * H, M, Dv, nsplit, combine, lambda, post, eps);                                  \
   } while (0)

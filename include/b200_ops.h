@@ -569,6 +569,7 @@ int b200_multimap_attn_mma(const void* q, const void* ck, const void* cv, const 
  * state row) or NULL (every token its own run, from pos / slot). A run at position 0 starts from zero state. ---- */
 int b200_short_conv(const float* x, long long ldx, const float* w, const float* state, const int* pos, const int* slot, float* y,
                     long long ldy, int tokens, int C, int taps, int act, void* stream);
+int b200_silu_rows(float* x, long long ld, long long rows, int cols, void* stream);
 int b200_short_conv_tail(const float* x, long long ldx, float* state, const int* runs, const int* pos, const int* slot, int n_runs,
                          int C, int taps, void* stream);
 int b200_delta_gates(float* q, long long ldq, float* k, long long ldk, float* a, long long lda, float* b, long long ldb,

@@ -42,7 +42,7 @@ from torch import nn
 from ..ops import elementwise as ew
 from ..ops.gemm import linear_exact
 from ..ops.hyper import gated_group_norm, hc_entry, hc_read, hc_step, xielu
-from ..ops.linear_scan import delta_gates, linear_scan, short_conv
+from ..ops.linear_scan import delta_gates, linear_scan, short_conv, silu_rows_
 from ..ops.multimap_attention import multimap_attention, qknorm_rope_store
 
 MAPS = 2                          # attention maps per head: fixed by the design
@@ -232,8 +232,9 @@ class DuratarLayer(nn.Module):
         H, D, Dv = m.heads, m.dim, m.vdim
         proj = linear_exact(h, self.in_proj, out_dtype=torch.float32)
         sl = lambda n: proj[:, self.parts[n][0]:self.parts[n][1]]             # noqa: E731
+        silu_rows_(proj[:, :self.parts["v"][1]])                              # q | k | v are the leading columns
         o = linear_scan(sl("q"), sl("k"), sl("v"), cache.state[self.idx][0], pos, slot, runs, n_runs, H, H, D, Dv, "decay",
-                        decay=self.decay, act=True)
+                        decay=self.decay)
         z = gated_group_norm(o, sl("g"), self.mix_norm, 1, eps, h.dtype)
         return linear_exact(z, self.o_proj, out_dtype=torch.float32)
 

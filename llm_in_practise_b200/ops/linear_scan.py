@@ -7,6 +7,7 @@ the per-layer state tensors (``inference.generate.PagedKVCache.state``). The tok
 own run (a decode batch, whose pos / slot are read on the device so that the step can be replayed from a CUDA graph). A
 run that starts at position 0 starts from a zero state, so state rows are reused without clearing.
 
+    silu_rows_     x <- silu(x) on a column slice of fp32 rows
     short_conv     y[t, c] = act(sum_j w[c, j] x[t - (taps - 1) + j, c]); the tail [rows, taps - 1, C] holds the last inputs
     delta_gates    unit q / k per head, decays exp(-exp(A_log) softplus(a + bias)), beta = sigmoid(b), in place
     linear_scan    mode "decay":  S <- decay_h S + k v^T;                                  o = S^T q
@@ -61,6 +62,19 @@ def short_conv(x: torch.Tensor, w: torch.Tensor, tail: torch.Tensor, pos: torch.
         y[first:first + n] = F.silu(acc) if act else acc
         tail[s] = ext[n:n + L]
     return y
+
+
+def silu_rows_(x: torch.Tensor) -> torch.Tensor:
+    """In place ``silu`` on an fp32 [T, C] view whose rows may be strided (a column slice of a fused projection)."""
+    if nv.use_native(x):
+        if x.dtype != torch.float32 or x.stride(1) != 1:
+            raise ValueError("silu_rows_: fp32 rows with a contiguous last dim")
+        fn = nv.proto("b200_silu_rows", [vp, i64, i64, i32, vp])
+        nv.check(fn(nv.ptr(x), x.stride(0), x.shape[0], x.shape[1], nv.stream()), "silu_rows")
+        nv.count_launch()
+        return x
+    x.copy_(F.silu(x))
+    return x
 
 
 def delta_gates(q: torch.Tensor, k: torch.Tensor, a: torch.Tensor, b: torch.Tensor, dt_bias: torch.Tensor, A_log: torch.Tensor,

@@ -102,13 +102,13 @@ def multimap_attention(q: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Te
         nsplit = 1
         if seen > 2 * _SPLIT_KEYS and T * G < 296:
             nsplit = min(32, -(-seen // _SPLIT_KEYS), max(1, 592 // (T * G)))
-        part = torch.empty(T * H * M * nsplit * (Dv + 2), dtype=torch.float32, device=q.device) if nsplit > 1 else None
+        part = torch.empty(T * H * M * nsplit * (Dv + 2), dtype=torch.float32, device=q.device) if nsplit * M > 1 else None
         fn = nv.proto("b200_multimap_attn", [vp, vp, vp, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, i32, f32, i32, i32,
                                              i32, i32, f32, f32, f32, i32, vp])
         nv.check(fn(nv.ptr(q), nv.ptr(cache_k), nv.ptr(cache_v), nv.ptr(pos), nv.ptr(slot), nv.ptr(table), table.shape[1],
                     nv.ptr(out), nv.ptr(part), T, H, G, M, D, Dv, BS, float(scale), int(window), int(keep_first), nsplit, int(combine),
                     float(lam), float(post), float(eps), nv.dtype_code(q.dtype), nv.stream()), "multimap_attn")
-        nv.count_launch(2 if nsplit > 1 else 1)
+        nv.count_launch(2 if nsplit * M > 1 else 1)
         return out
     rep = H // G
     pl, sl = pos.tolist(), slot.tolist()
