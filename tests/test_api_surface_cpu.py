@@ -1,5 +1,5 @@
 """Every keyword argument the reference's scripts pass to the HF / PEFT / quantisation entry points this framework mirrors is
-accepted by the mirror (an AST scan of /root/reference; skipped where that tree is absent)."""
+accepted by the mirror (an AST scan of /root/reference; skipped where that tree is absent or empty)."""
 import ast
 import dataclasses
 import glob
@@ -19,7 +19,7 @@ def _accepted(obj):
 
 
 def test_reference_call_sites_are_accepted():
-    if not os.path.isdir(REF):
+    if not os.path.isdir(os.path.join(REF, "Fine-Tuning")):
         pytest.skip("reference tree not present")
     from llm_in_practise_b200 import peft, quant
     from llm_in_practise_b200.data import datasets as D
@@ -59,7 +59,7 @@ def test_reference_call_sites_are_accepted():
 def test_distributed_training_call_sites_are_accepted():
     """Same scan over LLM_Distributed_Trainning/**: DDP / FSDP / fully_shard / MixedPrecision / DistributedSampler /
     deepspeed.initialize keyword arguments."""
-    if not os.path.isdir(REF):
+    if not os.path.isdir(os.path.join(REF, "Fine-Tuning")):
         pytest.skip("reference tree not present")
     from llm_in_practise_b200 import compat as C
     mirrors = {"DDP": C.DDP, "DistributedDataParallel": C.DDP, "FSDP": C.FSDP, "FullyShardedDataParallel": C.FSDP,
@@ -91,7 +91,7 @@ def test_distributed_training_call_sites_are_accepted():
 def test_methods_the_scripts_call_exist():
     """``model.<x>(...)`` / ``trainer.<x>(...)`` / ``peft_model.<x>(...)`` in the reference's scripts: each name exists on the
     object that plays that role here (``model`` is a causal LM, a PEFT wrapper or a GPTQModel depending on the script)."""
-    if not os.path.isdir(REF):
+    if not os.path.isdir(os.path.join(REF, "Fine-Tuning")):
         pytest.skip("reference tree not present")
     from llm_in_practise_b200.models.classifier import EncoderClassifier
     from llm_in_practise_b200.models.qwen3 import Qwen3ForCausalLM
