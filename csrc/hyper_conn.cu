@@ -19,15 +19,18 @@
 
 namespace b200 {
 
-constexpr int kMaxStreams = 8;
+constexpr int kMaxStreams = 16;
 
 // mode 0: write (y fp32) then read; 1: entry (y = embedding rows in dtype TE, normed by g_entry, copied to every stream)
 // then read; 2: read only.
-template <typename TH, typename TE>
+// SS: the stream count at compile time (1 .. 4: the streams of an element stay in registers), 0: any count up to kMaxStreams
+template <typename TH, typename TE, int SS>
 __global__ void __launch_bounds__(256)
 hc_step_kernel(const void* __restrict__ y_, const float* __restrict__ ls, float* __restrict__ X, const float* __restrict__ mix,
                const float* __restrict__ outc, const float* __restrict__ g_entry, const float* __restrict__ in_next,
-               const float* __restrict__ g_next, TH* __restrict__ h, float* __restrict__ xsum, int S, int W, float eps, int mode) {
+               const float* __restrict__ g_next, TH* __restrict__ h, float* __restrict__ xsum, int S_, int W, float eps, int mode) {
+  constexpr int NS = SS ? SS : kMaxStreams;
+  const int S = SS ? SS : S_;
   extern __shared__ float u_s[];                 // [W]
   __shared__ float red[32];
   __shared__ float cm[kMaxStreams * kMaxStreams], co[kMaxStreams], ci[kMaxStreams];
@@ -49,25 +52,31 @@ hc_step_kernel(const void* __restrict__ y_, const float* __restrict__ ls, float*
   __syncthreads();
   float ss = 0.f;
   for (int w = threadIdx.x; w < W; w += blockDim.x) {
-    float xo[kMaxStreams], xn[kMaxStreams];
+    float xo[NS], xn[NS];
     if (mode == 1) {
       const float v = to_f32<TE>(reinterpret_cast<const TE*>(y_)[t * W + w]) * entry_scale;
+#pragma unroll
       for (int s = 0; s < S; ++s) { xn[s] = v; xr[(long long)s * W + w] = v; }
     } else {
+#pragma unroll
       for (int s = 0; s < S; ++s) xo[s] = xr[(long long)s * W + w];
       if (mode == 0) {
         const float yv = reinterpret_cast<const float*>(y_)[t * W + w] * (ls ? ls[w] : 1.f);
+#pragma unroll
         for (int to = 0; to < S; ++to) {
           float a = co[to] * yv;
+#pragma unroll
           for (int s = 0; s < S; ++s) a = fmaf(cm[s * S + to], xo[s], a);
           xn[to] = a;
           xr[(long long)to * W + w] = a;
         }
       } else {
+#pragma unroll
         for (int s = 0; s < S; ++s) xn[s] = xo[s];
       }
     }
     float u = 0.f, sm = 0.f;
+#pragma unroll
     for (int s = 0; s < S; ++s) { u = fmaf(ci[s], xn[s], u); sm += xn[s]; }
     if (xsum) xsum[t * W + w] = sm;
     u_s[w] = u;
@@ -129,10 +138,15 @@ B200_API int b200_hc_step(const void* y, const float* ls, float* X, const float*
   if ((size_t)W * 4 > 200 * 1024) return B200_ERR_TOO_LARGE;
   const size_t smem = (size_t)W * 4;
   cudaStream_t st = (cudaStream_t)stream;
+#define HC_LAUNCH_S(TH, TE, SS)                                                                                            \
+  do {                                                                                                                     \
+    if (smem > 48 * 1024) B200_CHECK(cudaFuncSetAttribute(hc_step_kernel<TH, TE, SS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    hc_step_kernel<TH, TE, SS><<<(unsigned)tokens, 256, smem, st>>>(y, ls, X, mix, outc, g_entry, in_next, g_next, (TH*)h, xsum, S, W, eps, mode); \
+  } while (0)
 #define HC_LAUNCH(TH, TE)                                                                                                  \
   do {                                                                                                                     \
-    if (smem > 48 * 1024) B200_CHECK(cudaFuncSetAttribute(hc_step_kernel<TH, TE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-    hc_step_kernel<TH, TE><<<(unsigned)tokens, 256, smem, st>>>(y, ls, X, mix, outc, g_entry, in_next, g_next, (TH*)h, xsum, S, W, eps, mode); \
+    if (S == 1) HC_LAUNCH_S(TH, TE, 1); else if (S == 2) HC_LAUNCH_S(TH, TE, 2); else if (S == 3) HC_LAUNCH_S(TH, TE, 3);  \
+    else if (S == 4) HC_LAUNCH_S(TH, TE, 4); else HC_LAUNCH_S(TH, TE, 0);                                                  \
   } while (0)
   if (h_dtype == B200_DT_FP32) {
     if (e_dtype == B200_DT_FP32) HC_LAUNCH(float, float); else if (e_dtype == B200_DT_BF16) HC_LAUNCH(float, __nv_bfloat16); else HC_LAUNCH(float, __half);
@@ -142,6 +156,7 @@ B200_API int b200_hc_step(const void* y, const float* ls, float* X, const float*
     if (e_dtype == B200_DT_FP32) HC_LAUNCH(__half, float); else if (e_dtype == B200_DT_FP16) HC_LAUNCH(__half, __half); else return B200_ERR_UNSUPPORTED;
   }
 #undef HC_LAUNCH
+#undef HC_LAUNCH_S
   B200_LAUNCH_CHECK();
   return 0;
 }

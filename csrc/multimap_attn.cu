@@ -16,6 +16,7 @@
 //                          K/V reads, `nsplit` key ranges + a merge kernel for few tokens with many keys) and a scalar one
 //                          (a warp per (token, head)) for row sizes that are not whole chunks.
 #include "common.cuh"
+#include "mma_sync.cuh"
 #include "../include/b200_ops.h"
 
 #define B200_DISPATCH_T(dtype, ...)                                   \
@@ -198,8 +199,10 @@ multimap_attn_kernel(const T* __restrict__ q, const T* __restrict__ ck, const T*
 // inside the loop. Groups are merged by shuffles at the end, the four warps through shared memory. With one map and one
 // range the result is written directly; otherwise (max, sum, acc) go to `part` [tokens, H, M, nsplit, Dv + 2] and
 // multimap_attn_merge_kernel merges ranges and maps.
-template <typename T, int HB>
-__global__ void __launch_bounds__(128)
+// VC: value chunks per lane (2 when the value rows are wider than the key rows: a group then has only as many lanes as a key
+// row has chunks, covers twice the keys per instruction, and every lane accumulates chunks c and c + CP of the values)
+template <typename T, int HB, int VC>
+__global__ void __launch_bounds__(128, 4)               // four CTAs per SM: a decode batch of 64 x 4 groups x 2 maps is one wave
 multimap_attn_vec_kernel(const T* __restrict__ q, const T* __restrict__ ck, const T* __restrict__ cv, const int* __restrict__ pos,
                          const int* __restrict__ slot, const int* __restrict__ table, int max_blocks, T* __restrict__ out,
                          float* __restrict__ part, int H, int G, int M, int D, int Dv, int bs_log2, float scale, int window,
@@ -216,7 +219,10 @@ multimap_attn_vec_kernel(const T* __restrict__ q, const T* __restrict__ ck, cons
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int KPI = 32 / CP;
   const int kk = lane / CP, c = lane % CP;
-  const bool liveK = c < CPK, liveV = c < CPV;
+  const bool liveK = c < CPK;
+  bool liveV[VC];
+#pragma unroll
+  for (int x = 0; x < VC; ++x) liveV[x] = c + x * CP < CPV;
   const int p = pos[t];
   const int* trow = table + (long long)slot[t] * max_blocks;
   int lo = 0;
@@ -229,59 +235,89 @@ multimap_attn_vec_kernel(const T* __restrict__ q, const T* __restrict__ ck, cons
     i_lo = split * chunk;
     i_hi = min(total, i_lo + chunk);
   }
-  float qv[HB][E], acc[HB][E], mx[HB], l[HB];
+  // scores are kept in units of log 2 (scale * log2(e) is folded into q): one ex2 per exponential; the merge kernel reads
+  // the recorded maxima in the same units
+  const float sl2 = scale * 1.4426950408889634f;
+  float qv[HB][E], acc[HB][VC][E], mx[HB], l[HB];
 #pragma unroll
   for (int hh = 0; hh < HB; ++hh) {
     mx[hh] = -INFINITY;
     l[hh] = 0.f;
 #pragma unroll
     for (int e = 0; e < E; ++e) {
-      acc[hh][e] = 0.f;
-      qv[hh][e] = (liveK && hh < nh) ? to_f32<T>(q[(((long long)t * H + h0 + hh) * M + m) * D + c * E + e]) * scale : 0.f;
+#pragma unroll
+      for (int x = 0; x < VC; ++x) acc[hh][x][e] = 0.f;
+      qv[hh][e] = (liveK && hh < nh) ? to_f32<T>(q[(((long long)t * H + h0 + hh) * M + m) * D + c * E + e]) * sl2 : 0.f;
     }
   }
   const int bs_mask = (1 << bs_log2) - 1;
   const int stride = 4 * KPI;
   constexpr int U = HB >= 4 ? 2 : 4;
   for (int ib = i_lo; ib < i_hi; ib += stride * U) {
-    uint4 kr[U], vr[U];
+    uint4 kr[U], vr[U][VC];
     bool valid[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int i = ib + u * stride + warp * KPI + kk;
       valid[u] = i < i_hi;
-      kr[u] = vr[u] = make_uint4(0, 0, 0, 0);
+      kr[u] = make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int x = 0; x < VC; ++x) vr[u][x] = make_uint4(0, 0, 0, 0);
       if (valid[u]) {
         const int kp = i < n1 ? i : lo + (i - n1);
         const long long blk = trow[kp >> bs_log2];
         const int off = kp & bs_mask;
         if (liveK) kr[u] = *reinterpret_cast<const uint4*>(ck + ((((blk * G + g) * M + m) << bs_log2) + off) * D + c * E);
-        if (liveV) vr[u] = *reinterpret_cast<const uint4*>(cv + ((((blk * G) + g) << bs_log2) + off) * Dv + c * E);
+#pragma unroll
+        for (int x = 0; x < VC; ++x)
+          if (liveV[x]) vr[u][x] = *reinterpret_cast<const uint4*>(cv + ((((blk * G) + g) << bs_log2) + off) * Dv + (c + x * CP) * E);
       }
     }
+    // the U keys of a lane are scored first; the running maximum moves once per batch of U keys, so the accumulators are
+    // rescaled once per batch
+    float vf[U][VC][E], sc[U][HB];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      if (ib + u * stride >= i_hi) break;               // uniform over the CTA
-      float kf[E], vf[E];
+      float kf[E];
       const T* kp_ = reinterpret_cast<const T*>(&kr[u]);
-      const T* vp = reinterpret_cast<const T*>(&vr[u]);
 #pragma unroll
-      for (int e = 0; e < E; ++e) { kf[e] = to_f32<T>(kp_[e]); vf[e] = to_f32<T>(vp[e]); }
+      for (int e = 0; e < E; ++e) kf[e] = to_f32<T>(kp_[e]);
+#pragma unroll
+      for (int x = 0; x < VC; ++x) {
+        const T* vp = reinterpret_cast<const T*>(&vr[u][x]);
+#pragma unroll
+        for (int e = 0; e < E; ++e) vf[u][x][e] = to_f32<T>(vp[e]);
+      }
 #pragma unroll
       for (int hh = 0; hh < HB; ++hh) {
         float s = 0.f;
 #pragma unroll
         for (int e = 0; e < E; ++e) s = fmaf(qv[hh][e], kf[e], s);
         for (int o = CP >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-        if (valid[u]) {
-          const float mn = fmaxf(mx[hh], s);
-          const float r = expf(mx[hh] - mn);            // 0 on the first key (max = -inf)
-          const float pj = expf(s - mn);
-          mx[hh] = mn;
-          l[hh] = l[hh] * r + pj;
+        sc[u][hh] = valid[u] ? s : -INFINITY;
+      }
+    }
 #pragma unroll
-          for (int e = 0; e < E; ++e) acc[hh][e] = fmaf(pj, vf[e], acc[hh][e] * r);
-        }
+    for (int hh = 0; hh < HB; ++hh) {
+      float mn = mx[hh];
+#pragma unroll
+      for (int u = 0; u < U; ++u) mn = fmaxf(mn, sc[u][hh]);
+      const float ms = mn == -INFINITY ? 0.f : mn;       // no key of this lane yet: every term below is 2^(-inf) = 0
+      const float r = ex2_approx(mx[hh] - ms);
+      mx[hh] = mn;
+      l[hh] *= r;
+#pragma unroll
+      for (int x = 0; x < VC; ++x)
+#pragma unroll
+        for (int e = 0; e < E; ++e) acc[hh][x][e] *= r;
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const float pj = ex2_approx(sc[u][hh] - ms);
+        l[hh] += pj;
+#pragma unroll
+        for (int x = 0; x < VC; ++x)
+#pragma unroll
+          for (int e = 0; e < E; ++e) acc[hh][x][e] = fmaf(pj, vf[u][x][e], acc[hh][x][e]);
       }
     }
   }
@@ -292,23 +328,27 @@ multimap_attn_vec_kernel(const T* __restrict__ q, const T* __restrict__ ck, cons
       const float m2 = __shfl_xor_sync(0xffffffffu, mx[hh], o);
       const float l2 = __shfl_xor_sync(0xffffffffu, l[hh], o);
       const float mn = fmaxf(mx[hh], m2);
-      const float e1 = mx[hh] == -INFINITY ? 0.f : expf(mx[hh] - mn);
-      const float e2 = m2 == -INFINITY ? 0.f : expf(m2 - mn);
+      const float e1 = mx[hh] == -INFINITY ? 0.f : exp2f(mx[hh] - mn);
+      const float e2 = m2 == -INFINITY ? 0.f : exp2f(m2 - mn);
       l[hh] = l[hh] * e1 + l2 * e2;
 #pragma unroll
-      for (int e = 0; e < E; ++e) {
-        const float a2 = __shfl_xor_sync(0xffffffffu, acc[hh][e], o);
-        acc[hh][e] = acc[hh][e] * e1 + a2 * e2;
-      }
+      for (int x = 0; x < VC; ++x)
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          const float a2 = __shfl_xor_sync(0xffffffffu, acc[hh][x][e], o);
+          acc[hh][x][e] = acc[hh][x][e] * e1 + a2 * e2;
+        }
       mx[hh] = mn;
     }
     if (kk == 0) {
       float* w = sm + (warp * HB + hh) * LDW;
       if (c == 0) { w[0] = mx[hh]; w[1] = l[hh]; }
-      if (liveV) {
 #pragma unroll
-        for (int e = 0; e < E; ++e) w[2 + c * E + e] = acc[hh][e];
-      }
+      for (int x = 0; x < VC; ++x)
+        if (liveV[x]) {
+#pragma unroll
+          for (int e = 0; e < E; ++e) w[2 + (c + x * CP) * E + e] = acc[hh][x][e];
+        }
     }
   }
   __syncthreads();
@@ -324,7 +364,7 @@ multimap_attn_vec_kernel(const T* __restrict__ q, const T* __restrict__ ck, cons
     for (int w = 0; w < 4; ++w) {
       const float* ws = sm + (w * HB + hh) * LDW;
       if (ws[0] != -INFINITY) {
-        const float e = expf(ws[0] - mt);
+        const float e = exp2f(ws[0] - mt);
         lt += ws[1] * e;
         at += ws[2 + d] * e;
       }
@@ -361,7 +401,7 @@ multimap_attn_merge_kernel(const float* __restrict__ part, T* __restrict__ out, 
     for (int s = 0; s < nsplit; ++s) {
       const float ms = pr[s * LDW];
       if (ms == -INFINITY) continue;
-      const float e = expf(ms - mt);
+      const float e = exp2f(ms - mt);                    // the recorded maxima are in units of log 2
       lt += pr[s * LDW + 1] * e;
 #pragma unroll
       for (int a = 0; a < kAcc; ++a) {
@@ -425,8 +465,10 @@ B200_API int b200_multimap_attn(const void* q, const void* ck, const void* cv, c
     while ((1 << bs_log2) < block_size) ++bs_log2;
     if (D % E == 0 && Dv % E == 0 && CPK <= 32 && CPV <= 32 && (1 << bs_log2) == block_size && (part || (M == 1 && nsplit == 1)) &&
         !((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(ck) | reinterpret_cast<uintptr_t>(cv)) & 15)) {
+      // lanes per key: the chunks of a key row, or of half a value row if that is more (a lane then holds two value chunks)
       int CP = 1;
-      while (CP < CPK || CP < CPV) CP <<= 1;
+      while (CP < CPK || 2 * CP < CPV) CP <<= 1;
+      const int VC = CPV > CP ? 2 : 1;
       const int HB = rep >= 4 ? 4 : (rep >= 2 ? 2 : 1);
       const int passes = (rep + HB - 1) / HB;
       const bool direct = M == 1 && nsplit == 1;
@@ -434,9 +476,11 @@ B200_API int b200_multimap_attn(const void* q, const void* ck, const void* cv, c
       if (!direct && !part) return B200_ERR_BAD_SHAPE;
       dim3 grid(tokens, G * passes, nsplit * M);
       const size_t smem = (size_t)4 * HB * (Dv + 2) * sizeof(float);
-#define MMV(T, HBV)                                                                                                          \
-  multimap_attn_vec_kernel<T, HBV><<<grid, 128, smem, st>>>((const T*)q, (const T*)ck, (const T*)cv, pos, slot, table,        \
+#define MMV2(T, HBV, VCV)                                                                                                    \
+  multimap_attn_vec_kernel<T, HBV, VCV><<<grid, 128, smem, st>>>((const T*)q, (const T*)ck, (const T*)cv, pos, slot, table,   \
       max_blocks, (T*)out, part, H, G, M, D, Dv, bs_log2, scale, window, keep_first, nsplit, CP, CPK, CPV)
+#define MMV(T, HBV)                                                                                                          \
+  do { if (VC == 2) MMV2(T, HBV, 2); else MMV2(T, HBV, 1); } while (0)
 #define MMV_T(T)                                                                                                             \
   do {                                                                                                                       \
     if (HB == 4) MMV(T, 4); else if (HB == 2) MMV(T, 2); else MMV(T, 1);                                                     \
@@ -450,6 +494,7 @@ B200_API int b200_multimap_attn(const void* q, const void* ck, const void* cv, c
       else return B200_ERR_UNSUPPORTED;
 #undef MMV_T
 #undef MMV
+#undef MMV2
       B200_LAUNCH_CHECK();
       return 0;
     }

@@ -527,7 +527,7 @@ int b200_gemm_f32_exact(const float* A, const float* B, float* D, int M, int N, 
                         void* stream);
 
 /* ---- hyper-connected residual streams, xIELU, gated group norm (csrc/hyper_conn.cu) ----
- * X fp32 [tokens, S, W] (S <= 8). mode 0: x_t <- sum_s mix[s, t] x_s + out[t] * ls * y (y fp32 [tokens, W]; ls fp32 [W] or
+ * X fp32 [tokens, S, W] (S <= 16). mode 0: x_t <- sum_s mix[s, t] x_s + out[t] * ls * y (y fp32 [tokens, W]; ls fp32 [W] or
  * NULL), then u = sum_s in_next[s] x_s (NULL: ones) and h = u / sqrt(mean(u^2) + eps) * g_next[0] (h NULL: no read).
  * mode 1: y holds embedding rows (e_dtype) that are normed with g_entry[0] and copied into every stream first; mode 2: read
  * only. xsum: optional fp32 [tokens, W] that receives the sum of the streams. */

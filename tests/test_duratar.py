@@ -105,7 +105,7 @@ ODD = {
 # mechanisms alone
 # ------------------------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("device,dtype", CASES)
-@pytest.mark.parametrize("S,W", [(1, 40), (2, 72), (3, 64), (4, 100), (8, 24)])
+@pytest.mark.parametrize("S,W", [(1, 40), (2, 72), (3, 64), (4, 100), (8, 24), (13, 16)])
 def test_hyper_connection_steps(device, dtype, S, W):
     from llm_in_practise_b200.ops.hyper import hc_entry, hc_read, hc_step
     g = torch.Generator().manual_seed(S)
