@@ -102,7 +102,10 @@ __global__ void xielu_kernel(const T* __restrict__ z, T* __restrict__ y, long lo
 #pragma unroll
   for (int j = 0; j < V; ++j) {
     const float v = to_f32<T>(in[j]);
-    ov[j] = from_f32<T>(v > 0.f ? ap * v * v + 0.5f * v : aq * (expm1f(v) - v) + 0.5f * v);
+    // 16-bit outputs take the fast exponential (its error is far below their rounding); fp32 keeps expm1f, whose result
+    // stays accurate where exp(v) - 1 cancels
+    const float em1 = sizeof(T) == 4 ? expm1f(fminf(v, 0.f)) : __expf(fminf(v, 0.f)) - 1.f;
+    ov[j] = from_f32<T>(v > 0.f ? ap * v * v + 0.5f * v : aq * (em1 - v) + 0.5f * v);
   }
   if (V > 1) *reinterpret_cast<uint4*>(y + i) = *reinterpret_cast<const uint4*>(ov);
   else y[i] = ov[0];
