@@ -143,13 +143,13 @@ template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.as
 // grid (runs, H, column blocks); block = NW warps; a warp covers 32 / LPC columns, lane = l * (32 / LPC) + jj. The chunk of
 // tokens after the one being walked is already on its way into the other shared-memory buffer (cp.async), so the walk
 // waits for global memory once per run, not once per chunk. `vec`: rows of q / k / g start on 16-byte boundaries.
-template <int R, int MODE>
+template <int R, int MODE, int LPC>
 __global__ void __launch_bounds__(128)
 linear_scan_kernel(const float* __restrict__ q, long long ldq, const float* __restrict__ k, long long ldk,
                    const float* __restrict__ v, long long ldv, const float* __restrict__ g, long long ldg,
                    const float* __restrict__ beta, long long ldb, const float* __restrict__ decay, float* __restrict__ state,
                    const int* __restrict__ runs, const int* __restrict__ pos, const int* __restrict__ slot,
-                   float* __restrict__ o, int H, int G, int D, int Dv, int LPC, int act, int vec) {
+                   float* __restrict__ o, int H, int G, int D, int Dv, int act, int vec) {
   extern __shared__ __align__(16) float sm[];
   const int r_ = blockIdx.x, h = blockIdx.y;
   int first, n, p0, s;
@@ -157,7 +157,7 @@ linear_scan_kernel(const float* __restrict__ q, long long ldq, const float* __re
   else { first = r_; n = 1; p0 = pos[r_]; s = slot[r_]; }
   const int kvh = h / (H / G);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-  const int cpw = 32 / LPC;                               // columns per warp
+  constexpr int cpw = 32 / LPC;                           // columns per warp
   const int l = lane / cpw, jj = lane % cpw;
   const int ncol = nw * cpw;                              // columns per CTA
   const int col0 = blockIdx.z * ncol;
@@ -165,7 +165,7 @@ linear_scan_kernel(const float* __restrict__ q, long long ldq, const float* __re
   const bool live = j < Dv;
   const int row0 = l * R;
   constexpr int RP = R + 4;                               // a lane group's rows, padded so that the groups' 16-byte reads
-  const int DP = LPC * RP;                                // of one token fall into different banks
+  constexpr int DP = LPC * RP;                            // of one token fall into different banks
   auto at = [](int d) { return (d / R) * RP + d % R; };   // key channel d -> its place in a staged row
   const int ncp = (ncol + 3) & ~3;
   const int per = kScanChunk * DP * (MODE == 1 ? 3 : 2) + kScanChunk * ncp + kScanChunk;      // floats per buffer
@@ -237,6 +237,8 @@ linear_scan_kernel(const float* __restrict__ q, long long ldq, const float* __re
     const float* gs = GS(buf);
     const float* vs = VS(buf);
     const float* bs = BS(buf);
+    float* op = o + ((long long)(first + c0) * H + h) * Dv + j;
+    const long long ostride = (long long)H * Dv;
 #pragma unroll 2
     for (int tt = 0; tt < cn; ++tt) {
       float kr[R], qr[R];
@@ -268,6 +270,7 @@ linear_scan_kernel(const float* __restrict__ q, long long ldq, const float* __re
           d1 = fmaf(S[i + 1], kr[i + 1], d1);
         }
         float dot = d0 + d1;
+#pragma unroll
         for (int x = cpw; x < 32; x <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, x);
         const float u = bs[tt] * (vj - dot);
 #pragma unroll
@@ -279,8 +282,9 @@ linear_scan_kernel(const float* __restrict__ q, long long ldq, const float* __re
         }
       }
       float oacc = o0 + o1;
+#pragma unroll
       for (int x = cpw; x < 32; x <<= 1) oacc += __shfl_xor_sync(0xffffffffu, oacc, x);
-      if (l == 0 && live) o[((long long)(first + c0 + tt) * H + h) * Dv + j] = oacc;
+      if (l == 0 && live) op[(long long)tt * ostride] = oacc;
     }
     __syncthreads();
   }
@@ -364,17 +368,22 @@ B200_API int b200_linear_scan(const float* q, long long ldq, const float* k, lon
   const int vec = D % 4 == 0 && al(q, ldq) && al(k, ldk) && (mode == 0 || al(g, ldg));
   dim3 grid(n_runs, H, zb);
   cudaStream_t st = (cudaStream_t)stream;
-#define SCAN_K(RR, MM)                                                                                                     \
+#define SCAN_K(RR, MM, LL)                                                                                                 \
   do {                                                                                                                     \
-    auto kern = linear_scan_kernel<RR, MM>;                                                                                \
+    auto kern = linear_scan_kernel<RR, MM, LL>;                                                                            \
     if (smem > 48 * 1024) B200_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));  \
-    kern<<<grid, nw * 32, smem, st>>>(q, ldq, k, ldk, v, ldv, g, ldg, beta, ldb, decay, state, runs, pos, slot, o, H, G, D, Dv, LPC, act, vec); \
+    kern<<<grid, nw * 32, smem, st>>>(q, ldq, k, ldk, v, ldv, g, ldg, beta, ldb, decay, state, runs, pos, slot, o, H, G, D, Dv, act, vec); \
   } while (0)
-#define SCAN(RR)                                                                                                           \
+#define SCAN(RR, LL)                                                                                                       \
   do {                                                                                                                     \
-    if (mode == 0) SCAN_K(RR, 0); else SCAN_K(RR, 1);                                                                      \
+    if (mode == 0) SCAN_K(RR, 0, LL); else SCAN_K(RR, 1, LL);                                                              \
   } while (0)
-  if (R == 8) SCAN(8); else if (R == 16) SCAN(16); else SCAN(32);
+  if (R == 8) SCAN(8, 1);
+  else if (R == 16) {
+    if (LPC == 1) SCAN(16, 1); else if (LPC == 2) SCAN(16, 2); else if (LPC == 4) SCAN(16, 4); else if (LPC == 8) SCAN(16, 8); else SCAN(16, 16);
+  } else {
+    if (LPC == 16) SCAN(32, 16); else SCAN(32, 32);
+  }
 #undef SCAN
 #undef SCAN_K
   B200_LAUNCH_CHECK();
