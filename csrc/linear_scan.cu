@@ -174,6 +174,7 @@ linear_scan_kernel(const float* __restrict__ q, long long ldq, const float* __re
   auto GS = [&](int b) { return sm + b * per + 2 * kScanChunk * DP; };                         // MODE 1 only
   auto VS = [&](int b) { return sm + b * per + (MODE == 1 ? 3 : 2) * kScanChunk * DP; };       // [chunk][ncp]
   auto BS = [&](int b) { return VS(b) + kScanChunk * ncp; };                                   // [chunk]
+  float* os = sm + 2 * per;                               // [chunk][ncol][LPC]: per-lane parts of the read-outs of a chunk
   // padding rows (D <= d < DP) never arrive by copy: k = q = 0 (and a finite g) keep their state at zero
   if (LPC * R > D) {
     const int padw = LPC * R - D;
@@ -237,9 +238,9 @@ linear_scan_kernel(const float* __restrict__ q, long long ldq, const float* __re
     const float* gs = GS(buf);
     const float* vs = VS(buf);
     const float* bs = BS(buf);
-    float* op = o + ((long long)(first + c0) * H + h) * Dv + j;
-    const long long ostride = (long long)H * Dv;
-#pragma unroll 2
+    const float* vsp = vs + warp * cpw + jj;
+    float* osp = os + (warp * cpw + jj) * LPC + l;
+#pragma unroll 4
     for (int tt = 0; tt < cn; ++tt) {
       float kr[R], qr[R];
 #pragma unroll
@@ -247,7 +248,7 @@ linear_scan_kernel(const float* __restrict__ q, long long ldq, const float* __re
         *reinterpret_cast<float4*>(kr + i) = *reinterpret_cast<const float4*>(ks + tt * DP + l * RP + i);
         *reinterpret_cast<float4*>(qr + i) = *reinterpret_cast<const float4*>(qs + tt * DP + l * RP + i);
       }
-      const float vj = vs[tt * ncp + warp * cpw + jj];
+      const float vj = vsp[tt * ncp];
       float o0 = 0.f, o1 = 0.f;
       if (MODE == 0) {
 #pragma unroll
@@ -281,10 +282,17 @@ linear_scan_kernel(const float* __restrict__ q, long long ldq, const float* __re
           o1 = fmaf(S[i + 1], qr[i + 1], o1);
         }
       }
-      float oacc = o0 + o1;
+      // a token's read-out stays a per-lane part until the chunk is walked: nothing but the state (and, for the delta rule,
+      // the reduced S^T k) sits between one token and the next
+      osp[tt * ncol * LPC] = o0 + o1;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < cn * ncol; i += blockDim.x) {
+      const int tt = i / ncol, cc = i - tt * ncol;
+      float a = 0.f;
 #pragma unroll
-      for (int x = cpw; x < 32; x <<= 1) oacc += __shfl_xor_sync(0xffffffffu, oacc, x);
-      if (l == 0 && live) op[(long long)tt * ostride] = oacc;
+      for (int x = 0; x < LPC; ++x) a += os[i * LPC + x];
+      if (col0 + cc < Dv) o[((long long)(first + c0 + tt) * H + h) * Dv + col0 + cc] = a;
     }
     __syncthreads();
   }
@@ -362,7 +370,8 @@ B200_API int b200_linear_scan(const float* q, long long ldq, const float* k, lon
   const int zb = (Dv + ncol - 1) / ncol;
   const int DP = LPC * (R + 4);
   const int ncp = (ncol + 3) & ~3;
-  const size_t smem = 2 * ((size_t)kScanChunk * DP * (mode == 1 ? 3 : 2) + (size_t)kScanChunk * ncp + kScanChunk) * 4;
+  const size_t smem = (2 * ((size_t)kScanChunk * DP * (mode == 1 ? 3 : 2) + (size_t)kScanChunk * ncp + kScanChunk) +
+                       (size_t)kScanChunk * ncol * LPC) * 4;
   if (smem > 200 * 1024) return B200_ERR_TOO_LARGE;
   auto al = [](const void* p_, long long ld) { return !(reinterpret_cast<uintptr_t>(p_) & 15) && ld % 4 == 0; };
   const int vec = D % 4 == 0 && al(q, ldq) && al(k, ldk) && (mode == 0 || al(g, ldg));
