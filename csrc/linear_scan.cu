@@ -186,10 +186,14 @@ linear_scan_kernel(const float* __restrict__ q, long long ldq, const float* __re
       if (MODE == 1) GS(b)[x] = 0.f;
     }
   }
-  float S[R];
+  // the state rows of a thread as pairs: the walk runs on packed fp32 FMAs (two IEEE FMAs per instruction, same results)
+  float2 S2[R / 2];
   float* sp = state + (((long long)s * H + h) * D) * Dv;
 #pragma unroll
-  for (int i = 0; i < R; ++i) S[i] = (p0 > 0 && live && row0 + i < D) ? sp[(long long)(row0 + i) * Dv + j] : 0.f;
+  for (int i = 0; i < R / 2; ++i) {
+    S2[i].x = (p0 > 0 && live && row0 + 2 * i < D) ? sp[(long long)(row0 + 2 * i) * Dv + j] : 0.f;
+    S2[i].y = (p0 > 0 && live && row0 + 2 * i + 1 < D) ? sp[(long long)(row0 + 2 * i + 1) * Dv + j] : 0.f;
+  }
   const float dec = MODE == 0 ? decay[h] : 0.f;
 
   auto stage = [&](int b, int c0) {
@@ -242,46 +246,49 @@ linear_scan_kernel(const float* __restrict__ q, long long ldq, const float* __re
     float* osp = os + (warp * cpw + jj) * LPC + l;
 #pragma unroll 4
     for (int tt = 0; tt < cn; ++tt) {
-      float kr[R], qr[R];
+      float2 kr[R / 2], qr[R / 2];
 #pragma unroll
-      for (int i = 0; i < R; i += 4) {
-        *reinterpret_cast<float4*>(kr + i) = *reinterpret_cast<const float4*>(ks + tt * DP + l * RP + i);
-        *reinterpret_cast<float4*>(qr + i) = *reinterpret_cast<const float4*>(qs + tt * DP + l * RP + i);
+      for (int i = 0; i < R / 2; i += 2) {
+        const float4 k4 = *reinterpret_cast<const float4*>(ks + tt * DP + l * RP + 2 * i);
+        const float4 q4 = *reinterpret_cast<const float4*>(qs + tt * DP + l * RP + 2 * i);
+        kr[i] = make_float2(k4.x, k4.y); kr[i + 1] = make_float2(k4.z, k4.w);
+        qr[i] = make_float2(q4.x, q4.y); qr[i + 1] = make_float2(q4.z, q4.w);
       }
       const float vj = vsp[tt * ncp];
-      float o0 = 0.f, o1 = 0.f;
+      float2 oa = make_float2(0.f, 0.f), ob = make_float2(0.f, 0.f);
       if (MODE == 0) {
+        const float2 v2 = make_float2(vj, vj), dec2 = make_float2(dec, dec);
 #pragma unroll
-        for (int i = 0; i < R; i += 2) {
-          S[i] = fmaf(dec, S[i], kr[i] * vj);
-          S[i + 1] = fmaf(dec, S[i + 1], kr[i + 1] * vj);
-          o0 = fmaf(S[i], qr[i], o0);
-          o1 = fmaf(S[i + 1], qr[i + 1], o1);
+        for (int i = 0; i < R / 2; i += 2) {
+          S2[i] = __ffma2_rn(dec2, S2[i], __fmul2_rn(kr[i], v2));
+          S2[i + 1] = __ffma2_rn(dec2, S2[i + 1], __fmul2_rn(kr[i + 1], v2));
+          oa = __ffma2_rn(S2[i], qr[i], oa);
+          ob = __ffma2_rn(S2[i + 1], qr[i + 1], ob);
         }
       } else {
-        float gr[R];
+        float2 da = make_float2(0.f, 0.f), db = make_float2(0.f, 0.f);
 #pragma unroll
-        for (int i = 0; i < R; i += 4) *reinterpret_cast<float4*>(gr + i) = *reinterpret_cast<const float4*>(gs + tt * DP + l * RP + i);
-        float d0 = 0.f, d1 = 0.f;
-#pragma unroll
-        for (int i = 0; i < R; i += 2) {
-          S[i] *= gr[i];
-          S[i + 1] *= gr[i + 1];
-          d0 = fmaf(S[i], kr[i], d0);
-          d1 = fmaf(S[i + 1], kr[i + 1], d1);
+        for (int i = 0; i < R / 2; i += 2) {
+          const float4 g4 = *reinterpret_cast<const float4*>(gs + tt * DP + l * RP + 2 * i);
+          S2[i] = __fmul2_rn(S2[i], make_float2(g4.x, g4.y));
+          S2[i + 1] = __fmul2_rn(S2[i + 1], make_float2(g4.z, g4.w));
+          da = __ffma2_rn(S2[i], kr[i], da);
+          db = __ffma2_rn(S2[i + 1], kr[i + 1], db);
         }
-        float dot = d0 + d1;
+        float dot = (da.x + da.y) + (db.x + db.y);
 #pragma unroll
         for (int x = cpw; x < 32; x <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, x);
         const float u = bs[tt] * (vj - dot);
+        const float2 u2 = make_float2(u, u);
 #pragma unroll
-        for (int i = 0; i < R; i += 2) {
-          S[i] = fmaf(kr[i], u, S[i]);
-          S[i + 1] = fmaf(kr[i + 1], u, S[i + 1]);
-          o0 = fmaf(S[i], qr[i], o0);
-          o1 = fmaf(S[i + 1], qr[i + 1], o1);
+        for (int i = 0; i < R / 2; i += 2) {
+          S2[i] = __ffma2_rn(kr[i], u2, S2[i]);
+          S2[i + 1] = __ffma2_rn(kr[i + 1], u2, S2[i + 1]);
+          oa = __ffma2_rn(S2[i], qr[i], oa);
+          ob = __ffma2_rn(S2[i + 1], qr[i + 1], ob);
         }
       }
+      const float o0 = oa.x + oa.y, o1 = ob.x + ob.y;
       // a token's read-out stays a per-lane part until the chunk is walked: nothing but the state (and, for the delta rule,
       // the reduced S^T k) sits between one token and the next
       osp[tt * ncol * LPC] = o0 + o1;
@@ -298,8 +305,10 @@ linear_scan_kernel(const float* __restrict__ q, long long ldq, const float* __re
   }
   if (live) {
 #pragma unroll
-    for (int i = 0; i < R; ++i)
-      if (row0 + i < D) sp[(long long)(row0 + i) * Dv + j] = S[i];
+    for (int i = 0; i < R / 2; ++i) {
+      if (row0 + 2 * i < D) sp[(long long)(row0 + 2 * i) * Dv + j] = S2[i].x;
+      if (row0 + 2 * i + 1 < D) sp[(long long)(row0 + 2 * i + 1) * Dv + j] = S2[i].y;
+    }
   }
 }
 }  // namespace b200
