@@ -467,6 +467,31 @@ B200_API int b200_embedding_fwd(const long long* ids, const void* table, const v
   B200_LAUNCH_CHECK();
   return 0;
 }
+namespace b200 {
+// out[t, c] = table[ids[t], c] * scale + pos_table[pos[t], c]: embedding rows entering an fp32 stream with an additive
+// position table (fp32, built on the host) indexed by every token's own position
+template <typename T>
+__global__ void embedding_pos_kernel(const long long* __restrict__ ids, const T* __restrict__ table, float scale,
+                                     const int* __restrict__ pos, const float* __restrict__ pos_table, float* __restrict__ out,
+                                     int dim) {
+  const long long t = blockIdx.x;
+  const T* src = table + ids[t] * dim;
+  const float* ps = pos_table + (long long)pos[t] * dim;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) out[t * dim + i] = fmaf(to_f32<T>(src[i]), scale, ps[i]);
+}
+}  // namespace b200
+
+B200_API int b200_embedding_pos(const long long* ids, const void* table, float scale, const int* pos, const float* pos_table,
+                                float* out, long long tokens, int dim, int dtype, void* stream) {
+  using namespace b200;
+  if (tokens <= 0) return 0;
+  if (dim <= 0) return B200_ERR_BAD_SHAPE;
+  B200_DISPATCH_T(dtype, embedding_pos_kernel<T><<<(unsigned)tokens, 256, 0, (cudaStream_t)stream>>>(
+      ids, (const T*)table, scale, pos, pos_table, out, dim));
+  B200_LAUNCH_CHECK();
+  return 0;
+}
+
 B200_API int b200_embedding_bwd(const long long* ids, const void* dout, float* dtable, long long tokens, int dim,
                                 float scale, int dtype, void* stream) {
   if (tokens <= 0) return 0;

@@ -16,6 +16,16 @@
 //   b200_linear_scan       per head, state S [D, Dv] (fp32, in `state` [rows, H, D, Dv]):
 //                            mode 0  S <- decay_h S + k v^T ;                                   o = S^T q
 //                            mode 1  S <- diag(g) S ; u = beta (v - S^T k) ; S <- S + k u^T ;   o = S^T q
+//                            mode 2  S <- a_t S + b_t k v^T  (a, b one number per token and head) ;   o = S^T q
+//                          `ones` appends a column of ones to v (the state's last column is then the decayed sum of the
+//                          b_t k_t, and o's last column its product with q: the normaliser of an mLSTM read-out).
+//   b200_mlstm_gates       capped log gates of an mLSTM with their running maximum m (carried per sequence and head):
+//                          i = cap tanh((gi + bi) / cap), f = logsigmoid(cap tanh((gf + bf) / cap)), m' = max(f + m, i);
+//                          a = exp(f + m - m'), b = exp(i - m'), e = exp(-m'). m = 0 before position 0.
+//   b200_ssm_gates         step sizes of a selective state space: dt = softplus(x + bias), a = exp(-exp(A_log) dt), b = dt.
+//   b200_scan_readout      what follows a scan per token: optional division of each head by max(|last column|, e) + den_eps,
+//                          optional skip D_h x, optional silu gate BEFORE the norm, RMS norm over equal column groups,
+//                          weight (one per column, or shared by the groups), optional sigmoid gate AFTER the norm.
 //                          Columns of S are independent, so a thread owns R rows of one column, the lanes that share a
 //                          column reduce their partial dot products by shuffles, and a CTA owns a block of columns of one
 //                          (run, head): tokens are walked in order, staged through shared memory in chunks.
@@ -27,10 +37,11 @@ namespace b200 {
 __device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); }
 
 // V channels per thread (V = 4: rows of x, y, the tail and C are multiples of four floats on 16-byte boundaries)
-template <int V>
+template <int V, typename TY>
 __global__ void short_conv_kernel(const float* __restrict__ x, long long ldx, const float* __restrict__ w,
-                                  const float* __restrict__ state, const int* __restrict__ pos, const int* __restrict__ slot,
-                                  float* __restrict__ y, long long ldy, int tokens, int C, int taps, int act) {
+                                  const float* __restrict__ bias, const float* __restrict__ state, const int* __restrict__ pos,
+                                  const int* __restrict__ slot, TY* __restrict__ y, long long ldy, int tokens, int C, int taps,
+                                  int act, int residual) {
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const int CV = C / V;
   if (idx >= (long long)tokens * CV) return;
@@ -39,9 +50,9 @@ __global__ void short_conv_kernel(const float* __restrict__ x, long long ldx, co
   // nb: tokens of the same run right before t (at most taps - 1 matter)
   int nb = 0;
   while (nb < taps - 1 && t - nb - 1 >= 0 && slot[t - nb - 1] == s) ++nb;
-  float acc[V];
+  float acc[V], own[V];
 #pragma unroll
-  for (int e = 0; e < V; ++e) acc[e] = 0.f;
+  for (int e = 0; e < V; ++e) { acc[e] = bias ? bias[c + e] : 0.f; own[e] = 0.f; }
   for (int d = 0; d < taps; ++d) {                       // d tokens back
     if (p - d < 0) break;
     const float* src = d <= nb ? x + (long long)(t - d) * ldx + c : state + ((long long)s * (taps - 1) + (taps - 1 - (d - nb))) * C + c;
@@ -49,12 +60,19 @@ __global__ void short_conv_kernel(const float* __restrict__ x, long long ldx, co
     if (V == 4) *reinterpret_cast<float4*>(v) = *reinterpret_cast<const float4*>(src);
     else v[0] = src[0];
 #pragma unroll
-    for (int e = 0; e < V; ++e) acc[e] = fmaf(w[(long long)(c + e) * taps + (taps - 1 - d)], v[e], acc[e]);
+    for (int e = 0; e < V; ++e) {
+      acc[e] = fmaf(w[(long long)(c + e) * taps + (taps - 1 - d)], v[e], acc[e]);
+      if (d == 0) own[e] = v[e];
+    }
   }
 #pragma unroll
-  for (int e = 0; e < V; ++e) acc[e] = act ? silu_f(acc[e]) : acc[e];
-  if (V == 4) *reinterpret_cast<float4*>(y + (long long)t * ldy + c) = *reinterpret_cast<const float4*>(acc);
-  else y[(long long)t * ldy + c] = acc[0];
+  for (int e = 0; e < V; ++e) acc[e] = (act ? silu_f(acc[e]) : acc[e]) + (residual ? own[e] : 0.f);
+  TY* dst = y + (long long)t * ldy + c;
+  if (V == 4 && sizeof(TY) == 4) *reinterpret_cast<float4*>(dst) = *reinterpret_cast<const float4*>(acc);
+  else {
+#pragma unroll
+    for (int e = 0; e < V; ++e) dst[e] = from_f32<TY>(acc[e]);
+  }
 }
 
 constexpr int kMaxTaps = 16;
@@ -149,7 +167,8 @@ linear_scan_kernel(const float* __restrict__ q, long long ldq, const float* __re
                    const float* __restrict__ v, long long ldv, const float* __restrict__ g, long long ldg,
                    const float* __restrict__ beta, long long ldb, const float* __restrict__ decay, float* __restrict__ state,
                    const int* __restrict__ runs, const int* __restrict__ pos, const int* __restrict__ slot,
-                   float* __restrict__ o, int H, int G, int D, int Dv, int act, int vec) {
+                   float* __restrict__ o, int H, int G, int D, int Dv, int act, int vec, int ones) {
+  // MODE 2 reads its two per-token numbers through the pointers of mode 1's per-channel decays: g = a [T, H], beta = b [T, H]
   extern __shared__ __align__(16) float sm[];
   const int r_ = blockIdx.x, h = blockIdx.y;
   int first, n, p0, s;
@@ -168,12 +187,14 @@ linear_scan_kernel(const float* __restrict__ q, long long ldq, const float* __re
   constexpr int DP = LPC * RP;                            // of one token fall into different banks
   auto at = [](int d) { return (d / R) * RP + d % R; };   // key channel d -> its place in a staged row
   const int ncp = (ncol + 3) & ~3;
-  const int per = kScanChunk * DP * (MODE == 1 ? 3 : 2) + kScanChunk * ncp + kScanChunk;      // floats per buffer
+  const int vcols = Dv - ones;                            // columns that come from v; column vcols, if any, is all ones
+  const int per = kScanChunk * DP * (MODE == 1 ? 3 : 2) + kScanChunk * ncp + 2 * kScanChunk;  // floats per buffer
   auto KS = [&](int b) { return sm + b * per; };                                               // [chunk][DP]
   auto QS = [&](int b) { return sm + b * per + kScanChunk * DP; };
   auto GS = [&](int b) { return sm + b * per + 2 * kScanChunk * DP; };                         // MODE 1 only
   auto VS = [&](int b) { return sm + b * per + (MODE == 1 ? 3 : 2) * kScanChunk * DP; };       // [chunk][ncp]
   auto BS = [&](int b) { return VS(b) + kScanChunk * ncp; };                                   // [chunk]
+  auto AS = [&](int b) { return VS(b) + kScanChunk * ncp + kScanChunk; };                      // [chunk], MODE 2 only
   float* os = sm + 2 * per;                               // [chunk][ncol][LPC]: per-lane parts of the read-outs of a chunk
   // padding rows (D <= d < DP) never arrive by copy: k = q = 0 (and a finite g) keep their state at zero
   if (LPC * R > D) {
@@ -216,9 +237,13 @@ linear_scan_kernel(const float* __restrict__ q, long long ldq, const float* __re
           if (MODE == 1) cp_async4(GS(b) + tt * DP + at(d), gr + d);
         }
       }
-      const float* vr = v + tr * ldv + (long long)h * Dv + col0;
-      for (int cc = lane; cc < ncol && col0 + cc < Dv; cc += 32) cp_async4(VS(b) + tt * ncp + cc, vr + cc);
-      if (MODE == 1 && lane == 0) cp_async4(BS(b) + tt, beta + tr * ldb + h);
+      const float* vr = v + tr * ldv + (long long)h * vcols + col0;
+      for (int cc = lane; cc < ncol && col0 + cc < Dv; cc += 32) {
+        if (col0 + cc < vcols) cp_async4(VS(b) + tt * ncp + cc, vr + cc);
+        else VS(b)[tt * ncp + cc] = 1.f;
+      }
+      if (MODE >= 1 && lane == 0) cp_async4(BS(b) + tt, beta + tr * ldb + h);
+      if (MODE == 2 && lane == 1) cp_async4(AS(b) + tt, g + tr * ldg + h);
     }
   };
 
@@ -242,6 +267,7 @@ linear_scan_kernel(const float* __restrict__ q, long long ldq, const float* __re
     const float* gs = GS(buf);
     const float* vs = VS(buf);
     const float* bs = BS(buf);
+    const float* as = AS(buf);
     const float* vsp = vs + warp * cpw + jj;
     float* osp = os + (warp * cpw + jj) * LPC + l;
 #pragma unroll 4
@@ -254,10 +280,11 @@ linear_scan_kernel(const float* __restrict__ q, long long ldq, const float* __re
         kr[i] = make_float2(k4.x, k4.y); kr[i + 1] = make_float2(k4.z, k4.w);
         qr[i] = make_float2(q4.x, q4.y); qr[i + 1] = make_float2(q4.z, q4.w);
       }
-      const float vj = vsp[tt * ncp];
+      const float vj = MODE == 2 ? vsp[tt * ncp] * bs[tt] : vsp[tt * ncp];
       float2 oa = make_float2(0.f, 0.f), ob = make_float2(0.f, 0.f);
-      if (MODE == 0) {
-        const float2 v2 = make_float2(vj, vj), dec2 = make_float2(dec, dec);
+      if (MODE != 1) {
+        const float dt_ = MODE == 2 ? as[tt] : dec;
+        const float2 v2 = make_float2(vj, vj), dec2 = make_float2(dt_, dt_);
 #pragma unroll
         for (int i = 0; i < R / 2; i += 2) {
           S2[i] = __ffma2_rn(dec2, S2[i], __fmul2_rn(kr[i], v2));
@@ -311,21 +338,127 @@ linear_scan_kernel(const float* __restrict__ q, long long ldq, const float* __re
     }
   }
 }
+
+// One warp per (run, head). The gates of 32 tokens are formed in parallel; the maximum recurrence itself is walked in order
+// by every lane (two dependent operations per token), and lane j keeps what token j needs.
+__global__ void __launch_bounds__(128)
+mlstm_gates_kernel(const float* __restrict__ gi, long long ldi, const float* __restrict__ gf, long long ldf,
+                   const float* __restrict__ bi, const float* __restrict__ bf, float cap, float* __restrict__ mstate,
+                   const int* __restrict__ runs, const int* __restrict__ pos, const int* __restrict__ slot, int n_runs, int H,
+                   float* __restrict__ a, float* __restrict__ b, float* __restrict__ e) {
+  __shared__ float fs[4][32], is[4][32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long w = (long long)blockIdx.x * 4 + warp;
+  if (w >= (long long)n_runs * H) return;
+  const int r = (int)(w / H), h = (int)(w % H);
+  int first, n, p0, s;
+  if (runs) { first = runs[4 * r]; n = runs[4 * r + 1]; p0 = runs[4 * r + 2]; s = runs[4 * r + 3]; }
+  else { first = r; n = 1; p0 = pos[r]; s = slot[r]; }
+  float m = p0 > 0 ? mstate[(long long)s * H + h] : 0.f;
+  const float bih = bi[h], bfh = bf[h];
+  for (int c0 = 0; c0 < n; c0 += 32) {
+    const int cn = min(32, n - c0);
+    float fv = 0.f, iv = 0.f;
+    if (lane < cn) {
+      const long long t = first + c0 + lane;
+      iv = cap * tanhf((gi[t * ldi + h] + bih) / cap);
+      const float z = cap * tanhf((gf[t * ldf + h] + bfh) / cap);
+      fv = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));        // log sigmoid(z)
+    }
+    fs[warp][lane] = fv;
+    is[warp][lane] = iv;
+    __syncwarp();
+    float mprev = 0.f, mnew = 0.f;
+    for (int j = 0; j < cn; ++j) {
+      const float nm = fmaxf(fs[warp][j] + m, is[warp][j]);
+      if (j == lane) { mprev = m; mnew = nm; }
+      m = nm;
+    }
+    if (lane < cn) {
+      const long long t = first + c0 + lane;
+      a[t * H + h] = expf(fv + mprev - mnew);
+      b[t * H + h] = expf(iv - mnew);
+      e[t * H + h] = expf(-mnew);
+    }
+    __syncwarp();
+  }
+  if (lane == 0) mstate[(long long)s * H + h] = m;
+}
+
+__global__ void ssm_gates_kernel(const float* __restrict__ dt, long long ld, const float* __restrict__ dt_bias,
+                                 const float* __restrict__ A_log, float* __restrict__ a, float* __restrict__ b, long long tokens,
+                                 int H) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= tokens * H) return;
+  const long long t = idx / H;
+  const int h = (int)(idx - t * H);
+  const float z = dt[t * ld + h] + dt_bias[h];
+  const float sp = fmaxf(z, 0.f) + log1pf(expf(-fabsf(z)));  // softplus without a threshold
+  a[idx] = expf(-expf(A_log[h]) * sp);
+  b[idx] = sp;
+}
+
+// One CTA per token; the row [N = H * Dv] lives in shared memory between the passes. o rows have `ocols` columns per head
+// (Dv, or Dv + 1 when the scan carried a column of ones).
+template <typename TO>
+__global__ void __launch_bounds__(256)
+scan_readout_kernel(const float* __restrict__ o, int ocols, const float* __restrict__ e, float den_eps, float oscale,
+                    const float* __restrict__ skip, const float* __restrict__ x, long long ldx,
+                    const float* __restrict__ pre, long long ldpre, const float* __restrict__ post, long long ldpost,
+                    const float* __restrict__ w, int w_full, TO* __restrict__ out, int H, int Dv, int groups, float eps) {
+  extern __shared__ float row[];                         // [N] + [groups]
+  const long long t = blockIdx.x;
+  const int N = H * Dv, GS = N / groups;
+  float* gsum = row + N;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const float* orow = o + t * (long long)H * ocols;
+  for (int c = threadIdx.x; c < N; c += blockDim.x) {
+    const int h = c / Dv, d = c - h * Dv;
+    float v = orow[h * ocols + d] * oscale;
+    if (e) v = v / (fmaxf(fabsf(orow[h * ocols + Dv] * oscale), e[t * H + h]) + den_eps);
+    if (skip) v = fmaf(skip[h], x[t * ldx + c], v);
+    if (pre) { const float z = pre[t * ldpre + c]; v *= z / (1.f + expf(-z)); }
+    row[c] = v;
+  }
+  __syncthreads();
+  for (int g = warp; g < groups; g += nw) {
+    float ss = 0.f;
+    for (int i = lane; i < GS; i += 32) { const float v = row[g * GS + i]; ss = fmaf(v, v, ss); }
+    ss = warp_sum(ss);
+    if (lane == 0) gsum[g] = 1.f / sqrtf(ss / (float)GS + eps);
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < N; c += blockDim.x) {
+    float v = row[c] * gsum[c / GS] * w[w_full ? c : c % GS];
+    if (post) v *= 1.f / (1.f + expf(-post[t * ldpost + c]));
+    out[t * N + c] = from_f32<TO>(v);
+  }
+}
 }  // namespace b200
 
-B200_API int b200_short_conv(const float* x, long long ldx, const float* w, const float* state, const int* pos, const int* slot,
-                             float* y, long long ldy, int tokens, int C, int taps, int act, void* stream) {
+B200_API int b200_short_conv_ex(const float* x, long long ldx, const float* w, const float* bias, const float* state,
+                                const int* pos, const int* slot, void* y, long long ldy, int tokens, int C, int taps, int act,
+                                int residual, int y_dtype, void* stream) {
   using namespace b200;
   if (tokens <= 0) return 0;
   if (C <= 0 || taps < 1 || taps > kMaxTaps) return B200_ERR_BAD_SHAPE;
+  if (y_dtype != B200_DT_FP32 && y_dtype != B200_DT_BF16) return B200_ERR_UNSUPPORTED;
   cudaStream_t st = (cudaStream_t)stream;
   const bool vec = C % 4 == 0 && ldx % 4 == 0 && ldy % 4 == 0 &&
                    !((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(state)) & 15);
   const long long n = (long long)tokens * (vec ? C / 4 : C);
-  if (vec) short_conv_kernel<4><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(x, ldx, w, state, pos, slot, y, ldy, tokens, C, taps, act);
-  else short_conv_kernel<1><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(x, ldx, w, state, pos, slot, y, ldy, tokens, C, taps, act);
+  const unsigned grid = (unsigned)((n + 255) / 256);
+#define CONV(VV, TY) short_conv_kernel<VV, TY><<<grid, 256, 0, st>>>(x, ldx, w, bias, state, pos, slot, (TY*)y, ldy, tokens, C, taps, act, residual)
+  if (y_dtype == B200_DT_FP32) { if (vec) CONV(4, float); else CONV(1, float); }
+  else { if (vec) CONV(4, __nv_bfloat16); else CONV(1, __nv_bfloat16); }
+#undef CONV
   B200_LAUNCH_CHECK();
   return 0;
+}
+
+B200_API int b200_short_conv(const float* x, long long ldx, const float* w, const float* state, const int* pos, const int* slot,
+                             float* y, long long ldy, int tokens, int C, int taps, int act, void* stream) {
+  return b200_short_conv_ex(x, ldx, w, nullptr, state, pos, slot, y, ldy, tokens, C, taps, act, 0, B200_DT_FP32, stream);
 }
 
 B200_API int b200_silu_rows(float* x, long long ld, long long rows, int cols, void* stream) {
@@ -363,10 +496,11 @@ B200_API int b200_delta_gates(float* q, long long ldq, float* k, long long ldk, 
 B200_API int b200_linear_scan(const float* q, long long ldq, const float* k, long long ldk, const float* v, long long ldv,
                               const float* g, long long ldg, const float* beta, long long ldb, const float* decay, float* state,
                               const int* runs, const int* pos, const int* slot, int n_runs, float* o, int H, int G, int D, int Dv,
-                              int mode, int act, void* stream) {
+                              int mode, int act, int ones, void* stream) {
   using namespace b200;
   if (n_runs <= 0) return 0;
-  if (H <= 0 || G <= 0 || H % G || D <= 0 || Dv <= 0 || mode < 0 || mode > 1 || H > 65535) return B200_ERR_BAD_SHAPE;
+  if (H <= 0 || G <= 0 || H % G || D <= 0 || Dv <= 0 || mode < 0 || mode > 2 || H > 65535 || ones < 0 || ones > 1 || Dv - ones < 1)
+    return B200_ERR_BAD_SHAPE;
   // rows per thread R in {8, 16, 32}; lanes per column LPC = power of two with LPC * R >= D
   int R = D <= 8 ? 8 : (D <= 256 ? 16 : 32);
   int LPC = 1;
@@ -379,22 +513,22 @@ B200_API int b200_linear_scan(const float* q, long long ldq, const float* k, lon
   const int zb = (Dv + ncol - 1) / ncol;
   const int DP = LPC * (R + 4);
   const int ncp = (ncol + 3) & ~3;
-  const size_t smem = (2 * ((size_t)kScanChunk * DP * (mode == 1 ? 3 : 2) + (size_t)kScanChunk * ncp + kScanChunk) +
+  const size_t smem = (2 * ((size_t)kScanChunk * DP * (mode == 1 ? 3 : 2) + (size_t)kScanChunk * ncp + 2 * kScanChunk) +
                        (size_t)kScanChunk * ncol * LPC) * 4;
   if (smem > 200 * 1024) return B200_ERR_TOO_LARGE;
   auto al = [](const void* p_, long long ld) { return !(reinterpret_cast<uintptr_t>(p_) & 15) && ld % 4 == 0; };
-  const int vec = D % 4 == 0 && al(q, ldq) && al(k, ldk) && (mode == 0 || al(g, ldg));
+  const int vec = D % 4 == 0 && al(q, ldq) && al(k, ldk) && (mode != 1 || al(g, ldg));
   dim3 grid(n_runs, H, zb);
   cudaStream_t st = (cudaStream_t)stream;
 #define SCAN_K(RR, MM, LL)                                                                                                 \
   do {                                                                                                                     \
     auto kern = linear_scan_kernel<RR, MM, LL>;                                                                            \
     if (smem > 48 * 1024) B200_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));  \
-    kern<<<grid, nw * 32, smem, st>>>(q, ldq, k, ldk, v, ldv, g, ldg, beta, ldb, decay, state, runs, pos, slot, o, H, G, D, Dv, act, vec); \
+    kern<<<grid, nw * 32, smem, st>>>(q, ldq, k, ldk, v, ldv, g, ldg, beta, ldb, decay, state, runs, pos, slot, o, H, G, D, Dv, act, vec, ones); \
   } while (0)
 #define SCAN(RR, LL)                                                                                                       \
   do {                                                                                                                     \
-    if (mode == 0) SCAN_K(RR, 0, LL); else SCAN_K(RR, 1, LL);                                                              \
+    if (mode == 0) SCAN_K(RR, 0, LL); else if (mode == 1) SCAN_K(RR, 1, LL); else SCAN_K(RR, 2, LL);                       \
   } while (0)
   if (R == 8) SCAN(8, 1);
   else if (R == 16) {
@@ -404,6 +538,56 @@ B200_API int b200_linear_scan(const float* q, long long ldq, const float* k, lon
   }
 #undef SCAN
 #undef SCAN_K
+  B200_LAUNCH_CHECK();
+  return 0;
+}
+
+B200_API int b200_mlstm_gates(const float* gi, long long ldi, const float* gf, long long ldf, const float* bi, const float* bf,
+                              float cap, float* mstate, const int* runs, const int* pos, const int* slot, int n_runs, int H,
+                              float* a, float* b, float* e, void* stream) {
+  using namespace b200;
+  if (n_runs <= 0) return 0;
+  if (H <= 0 || !(cap > 0.f)) return B200_ERR_BAD_SHAPE;
+  const long long warps = (long long)n_runs * H;
+  mlstm_gates_kernel<<<(unsigned)((warps + 3) / 4), 128, 0, (cudaStream_t)stream>>>(gi, ldi, gf, ldf, bi, bf, cap, mstate, runs, pos,
+                                                                                    slot, n_runs, H, a, b, e);
+  B200_LAUNCH_CHECK();
+  return 0;
+}
+
+B200_API int b200_ssm_gates(const float* dt, long long ld, const float* dt_bias, const float* A_log, float* a, float* b,
+                            long long tokens, int H, void* stream) {
+  using namespace b200;
+  if (tokens <= 0) return 0;
+  if (H <= 0) return B200_ERR_BAD_SHAPE;
+  const long long n = tokens * H;
+  ssm_gates_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(dt, ld, dt_bias, A_log, a, b, tokens, H);
+  B200_LAUNCH_CHECK();
+  return 0;
+}
+
+B200_API int b200_scan_readout(const float* o, int ocols, const float* e, float den_eps, float oscale, const float* skip,
+                               const float* x, long long ldx, const float* pre, long long ldpre, const float* post,
+                               long long ldpost, const float* w, int w_full, void* out, long long tokens, int H, int Dv,
+                               int groups, float eps, int out_dtype, void* stream) {
+  using namespace b200;
+  if (tokens <= 0) return 0;
+  if (H <= 0 || Dv <= 0 || groups <= 0 || (H * Dv) % groups || ocols < Dv || (e && ocols < Dv + 1) || (skip && !x))
+    return B200_ERR_BAD_SHAPE;
+  const size_t smem = ((size_t)H * Dv + groups) * sizeof(float);
+  if (smem > 200 * 1024) return B200_ERR_TOO_LARGE;
+  cudaStream_t st = (cudaStream_t)stream;
+#define READOUT(TO)                                                                                                          \
+  do {                                                                                                                       \
+    auto kern = scan_readout_kernel<TO>;                                                                                     \
+    if (smem > 48 * 1024) B200_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));    \
+    kern<<<(unsigned)tokens, 256, smem, st>>>(o, ocols, e, den_eps, oscale, skip, x, ldx, pre, ldpre, post, ldpost, w, w_full,  \
+                                              (TO*)out, H, Dv, groups, eps);                                                 \
+  } while (0)
+  if (out_dtype == B200_DT_FP32) READOUT(float);
+  else if (out_dtype == B200_DT_BF16) READOUT(__nv_bfloat16);
+  else return B200_ERR_UNSUPPORTED;
+#undef READOUT
   B200_LAUNCH_CHECK();
   return 0;
 }

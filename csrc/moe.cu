@@ -4,7 +4,7 @@
 //                      experts per token and their weights. mode 0: softmax over the chosen logits only; mode 1: softmax
 //                      over all experts, chosen probabilities kept as they are; mode 2: mode 1 renormalised to sum 1.
 //                      One warp per token; ties go to the lower expert index.
-//   b200_moe_route_grouped   sigmoid router with group-limited choice: s = sigmoid(W_r h); the choice is made on
+//   b200_moe_route_grouped   router with group-limited choice: s = sigmoid(W_r h) (or softmax over the experts); the choice is made on
 //                      s + correction, only among the experts of the `keep` groups (of `groups` equal runs of neighbours)
 //                      whose `group_top` largest choice scores sum highest; the weights are s of the chosen experts, as
 //                      they are or renormalised to sum 1. Rows of W_r past the experts are per-token gates: their sigmoid
@@ -65,7 +65,7 @@ template <typename TH, typename TW>
 __global__ void __launch_bounds__(128)
 moe_route_grouped_kernel(const TH* __restrict__ h, const TW* __restrict__ wr, const float* __restrict__ corr,
                          long long* __restrict__ top_i, float* __restrict__ top_p, float* __restrict__ gate_out, long long tokens,
-                         int W, int E, int X, int top, int groups, int keep, int group_top, int renorm) {
+                         int W, int E, int X, int top, int groups, int keep, int group_top, int renorm, int softmax) {
   extern __shared__ float zbuf[];                     // per warp: s [E + X], choice [E], group score [groups]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long t = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
@@ -79,10 +79,16 @@ moe_route_grouped_kernel(const TH* __restrict__ h, const TW* __restrict__ wr, co
     float a = 0.f;
     for (int i = lane; i < W; i += 32) a = fmaf(to_f32<TH>(hr[i]), to_f32<TW>(w[i]), a);
     a = warp_sum(a);
-    if (lane == 0) s[e] = 1.f / (1.f + expf(-a));
+    if (lane == 0) s[e] = (softmax && e < E) ? a : 1.f / (1.f + expf(-a));
   }
   __syncwarp();
   if (lane != 0) return;
+  if (softmax) {                                       // scores are the softmax of the logits over all experts
+    float zmax = -INFINITY, zsum = 0.f;
+    for (int e = 0; e < E; ++e) zmax = fmaxf(zmax, s[e]);
+    for (int e = 0; e < E; ++e) { s[e] = expf(s[e] - zmax); zsum += s[e]; }
+    for (int e = 0; e < E; ++e) s[e] /= zsum;
+  }
   for (int x = 0; x < X; ++x) gate_out[t * X + x] = s[E + x];
   for (int e = 0; e < E; ++e) choice[e] = s[e] + (corr ? corr[e] : 0.f);
   const int per = E / groups;
@@ -173,7 +179,7 @@ B200_API int b200_moe_route(const void* h, const void* wr, const float* bias, lo
 
 B200_API int b200_moe_route_grouped(const void* h, const void* wr, const float* corr, long long* top_i, float* top_p,
                                     float* gate_out, long long tokens, int W, int E, int X, int top, int groups, int keep,
-                                    int group_top, int renorm, int h_dtype, int w_dtype, void* stream) {
+                                    int group_top, int renorm, int softmax, int h_dtype, int w_dtype, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
   if (tokens <= 0) return 0;
   if (W <= 0 || E <= 0 || X < 0 || top <= 0 || top > E || E > 2048 || groups <= 0 || E % groups || keep <= 0 || keep > groups ||
@@ -185,7 +191,7 @@ B200_API int b200_moe_route_grouped(const void* h, const void* wr, const float* 
   typedef __nv_bfloat16 bf;
 #define RG(TH, TW)                                                                                                          \
   moe_route_grouped_kernel<TH, TW><<<grid, warps * 32, smem, st>>>((const TH*)h, (const TW*)wr, corr, top_i, top_p, gate_out,    \
-                                                                  tokens, W, E, X, top, groups, keep, group_top, renorm)
+                                                                  tokens, W, E, X, top, groups, keep, group_top, renorm, softmax)
   if (h_dtype == B200_DT_BF16 && w_dtype == B200_DT_BF16) RG(bf, bf);
   else if (h_dtype == B200_DT_BF16 && w_dtype == B200_DT_FP32) RG(bf, float);
   else if (h_dtype == B200_DT_FP32 && w_dtype == B200_DT_FP32) RG(float, float);

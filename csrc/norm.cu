@@ -425,55 +425,70 @@ B200_API int b200_norm_bwd_noalloc(int layer_norm, const void* dy, const void* h
 // kept in shared memory between the passes, all statistics and the stream itself are fp32.
 // ---------------------------------------------------------------------------------------------
 namespace b200 {
+// `center` 1: both norms take the row's mean off first and divide by the root of the variance (a layer norm with a weight and
+// no bias); the statistics are two passes over the row in shared memory (mean, then squared deviations).
 template <typename TY, typename TH, typename WT>
 __global__ void __launch_bounds__(kNormThreads)
 sandwich_norm_kernel(const TY* __restrict__ y, const WT* __restrict__ w_post, const float* __restrict__ res_in,
                      float* __restrict__ res_out, const WT* __restrict__ w_next, TH* __restrict__ h, int cols, float eps,
-                     float off, float mult) {
+                     float off, float mult, int center) {
   extern __shared__ float rowbuf[];
   __shared__ float red[32];
   const long long row = blockIdx.x;
-  float ss = 0.f;
+  float ss = 0.f, s1 = 0.f;
   if (y) {
     const TY* yr = y + row * cols;
     for (int i = threadIdx.x; i < cols; i += blockDim.x) {
       const float v = to_f32<TY>(yr[i]);
       rowbuf[i] = v;
       ss += v * v;
+      s1 += v;
     }
   } else {
     for (int i = threadIdx.x; i < cols; i += blockDim.x) rowbuf[i] = 0.f;
   }
-  float r1 = 1.f;
+  float r1 = 1.f, m1 = 0.f;
   if (w_post) {
+    if (center) {
+      m1 = block_sum(s1, red) / (float)cols;
+      ss = 0.f;
+      for (int i = threadIdx.x; i < cols; i += blockDim.x) { const float d = rowbuf[i] - m1; ss += d * d; }
+    }
     ss = block_sum(ss, red);
     r1 = 1.f / sqrtf(ss / (float)cols + eps);
   }
   __syncthreads();
-  float s2 = 0.f;
+  float s2 = 0.f, t1 = 0.f;
   for (int i = threadIdx.x; i < cols; i += blockDim.x) {
     float v = rowbuf[i];
-    if (w_post) v = v * r1 * (off + to_f32<WT>(w_post[i]));
+    if (w_post) v = (v - m1) * r1 * (off + to_f32<WT>(w_post[i]));
     v *= mult;
     if (res_in) v += res_in[row * cols + i];
     rowbuf[i] = v;
     if (res_out) res_out[row * cols + i] = v;
     s2 += v * v;
+    t1 += v;
   }
   if (!w_next) {                                        // no norm follows: h, if asked for, is the stream in the next GEMM's dtype
     if (h)
       for (int i = threadIdx.x; i < cols; i += blockDim.x) h[row * cols + i] = from_f32<TH>(rowbuf[i]);
     return;
   }
+  float m2 = 0.f;
+  if (center) {
+    m2 = block_sum(t1, red) / (float)cols;
+    s2 = 0.f;
+    for (int i = threadIdx.x; i < cols; i += blockDim.x) { const float d = rowbuf[i] - m2; s2 += d * d; }
+  }
   s2 = block_sum(s2, red);
   const float r2 = 1.f / sqrtf(s2 / (float)cols + eps);
   for (int i = threadIdx.x; i < cols; i += blockDim.x)
-    h[row * cols + i] = from_f32<TH>(rowbuf[i] * r2 * (off + to_f32<WT>(w_next[i])));
+    h[row * cols + i] = from_f32<TH>((rowbuf[i] - m2) * r2 * (off + to_f32<WT>(w_next[i])));
 }
 
 template <typename TY, typename TH, typename WT>
 static int sandwich_launch(const void* y, const void* w_post, const float* res_in, float* res_out, const void* w_next, void* h,
-                           long long rows, int cols, float eps, float off, float mult, cudaStream_t st) {
+                           long long rows, int cols, float eps, float off, float mult, int center, cudaStream_t st) {
   const size_t smem = (size_t)cols * sizeof(float);
   auto kern = sandwich_norm_kernel<TY, TH, WT>;
   if (smem > 48 * 1024) {
@@ -481,21 +496,21 @@ static int sandwich_launch(const void* y, const void* w_post, const float* res_i
     B200_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   }
   kern<<<(unsigned)rows, kNormThreads, smem, st>>>((const TY*)y, (const WT*)w_post, res_in, res_out, (const WT*)w_next, (TH*)h,
-                                                   cols, eps, off, mult);
+                                                   cols, eps, off, mult, center);
   B200_LAUNCH_CHECK();
   return 0;
 }
 }  // namespace b200
 
-B200_API int b200_sandwich_norm(const void* y, const void* w_post, const float* res_in, float* res_out, const void* w_next,
-                                void* h, long long rows, int cols, float eps, float off, float mult, int y_dtype, int h_dtype,
-                                int w_dtype, void* stream) {
+B200_API int b200_sandwich_norm_c(const void* y, const void* w_post, const float* res_in, float* res_out, const void* w_next,
+                                  void* h, long long rows, int cols, float eps, float off, float mult, int center, int y_dtype,
+                                  int h_dtype, int w_dtype, void* stream) {
   using namespace b200;
   cudaStream_t st = (cudaStream_t)stream;
   if (rows <= 0) return 0;
   if (cols <= 0) return B200_ERR_BAD_SHAPE;
   typedef __nv_bfloat16 bf;
-#define SW(TY, TH, WT) return sandwich_launch<TY, TH, WT>(y, w_post, res_in, res_out, w_next, h, rows, cols, eps, off, mult, st)
+#define SW(TY, TH, WT) return sandwich_launch<TY, TH, WT>(y, w_post, res_in, res_out, w_next, h, rows, cols, eps, off, mult, center, st)
   if (w_dtype == B200_DT_BF16) {
     if (y_dtype == B200_DT_FP32 && h_dtype == B200_DT_BF16) SW(float, bf, bf);
     if (y_dtype == B200_DT_BF16 && h_dtype == B200_DT_BF16) SW(bf, bf, bf);
@@ -508,4 +523,11 @@ B200_API int b200_sandwich_norm(const void* y, const void* w_post, const float* 
   }
 #undef SW
   return B200_ERR_UNSUPPORTED;
+}
+
+B200_API int b200_sandwich_norm(const void* y, const void* w_post, const float* res_in, float* res_out, const void* w_next,
+                                void* h, long long rows, int cols, float eps, float off, float mult, int y_dtype, int h_dtype,
+                                int w_dtype, void* stream) {
+  return b200_sandwich_norm_c(y, w_post, res_in, res_out, w_next, h, rows, cols, eps, off, mult, 0, y_dtype, h_dtype, w_dtype,
+                              stream);
 }

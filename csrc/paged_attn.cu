@@ -73,13 +73,13 @@ rope_paged_store_kernel(T* __restrict__ qkv, long long row_stride, const float* 
       const long long base = (((long long)blk * G + g) * block_size + off) * D;
       ck[base + d0] = from_f32<T>(ru);
       if (has1) ck[base + d1] = from_f32<T>(rv);
-      if (v_from_k) {
+      if (v_from_k && cv) {                             // cv NULL: no value pool (the key rows are read as values)
         cv[base + d0] = from_f32<T>(u);
         if (has1) cv[base + d1] = from_f32<T>(v);
       }
     }
   }
-  if (!v_from_k) {
+  if (!v_from_k && cv) {
     const T* vsrc = row + (long long)(H + G) * D;
     for (int w = threadIdx.x; w < G * D; w += blockDim.x) {
       const int g = w / D, d = w % D;

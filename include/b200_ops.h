@@ -183,6 +183,9 @@ int b200_gelu_fwd(const void* x, void* y, long long n, int dtype, void* stream);
 int b200_gelu_bwd(const void* dy, const void* x, void* dx, long long n, int dtype, void* stream);
 int b200_embedding_fwd(const long long* ids, const void* table, const void* pos_table, void* out, long long tokens,
                        int dim, int period, float scale, int dtype, void* stream);
+/* out fp32 [tokens, dim] = table[ids[t]] * scale + pos_table[pos[t]] (pos_table fp32 [positions, dim]). */
+int b200_embedding_pos(const long long* ids, const void* table, float scale, const int* pos, const float* pos_table, float* out,
+                       long long tokens, int dim, int dtype, void* stream);
 int b200_embedding_bwd(const long long* ids, const void* dout, float* dtable, long long tokens, int dim, float scale,
                        int dtype, void* stream);
 int b200_dropout(const void* x, void* y, long long n, unsigned long long seed, float p, int dtype, void* stream);
@@ -473,6 +476,10 @@ int b200_paged_attn_mma(const void* q, long long q_stride, const void* ck, const
 int b200_sandwich_norm(const void* y, const void* w_post, const float* res_in, float* res_out, const void* w_next, void* h,
                        long long rows, int cols, float eps, float off, float mult, int y_dtype, int h_dtype, int w_dtype,
                        void* stream);
+/* The same with `center` 1: both norms are layer norms without a bias ((x - mean) / sqrt(variance + eps) * (off + w)). */
+int b200_sandwich_norm_c(const void* y, const void* w_post, const float* res_in, float* res_out, const void* w_next, void* h,
+                         long long rows, int cols, float eps, float off, float mult, int center, int y_dtype, int h_dtype,
+                         int w_dtype, void* stream);
 /* y [rows, F] = g * sigmoid(alpha * g) * (u + shift), g = min(gate, limit), u = clamp(up, +-limit) over gu [rows, 2F]
  * (gate | up); limit <= 0: no clamps. */
 int b200_clamped_glu(const void* gu, void* y, long long rows, int F, float limit, float alpha, float shift, int dtype, void* stream);
@@ -483,13 +490,14 @@ int b200_softcap(float* x, long long n, float cap, void* stream);
  * logits_out: optional fp32 [tokens, E]. */
 int b200_moe_route(const void* h, const void* wr, const float* bias, long long* top_i, float* top_p, float* logits_out,
                    long long tokens, int W, int E, int top, int mode, int h_dtype, int w_dtype, void* stream);
-/* Sigmoid router with group-limited choice, fp32: s = sigmoid(h W_r^T); choice = s + corr (corr fp32 [E] or NULL); only
+/* Router with group-limited choice, fp32: s = sigmoid(h W_r^T), or with `softmax` 1 the softmax of the experts' logits;
+ * choice = s + corr (corr fp32 [E] or NULL); only
  * experts of the `keep` groups (of `groups` equal runs of neighbouring experts) whose `group_top` largest choice scores
  * sum highest can be chosen; top_p = s of the chosen (renorm: divided by their sum). W_r has E + X rows: the sigmoid of
  * the last X goes to gate_out fp32 [tokens, X] (per-token gates, e.g. of a shared expert). */
 int b200_moe_route_grouped(const void* h, const void* wr, const float* corr, long long* top_i, float* top_p, float* gate_out,
                            long long tokens, int W, int E, int X, int top, int groups, int keep, int group_top, int renorm,
-                           int h_dtype, int w_dtype, void* stream);
+                           int softmax, int h_dtype, int w_dtype, void* stream);
 /* out fp32 [tokens, W] = sum_k p[t, k] * y[dest[t * top + k]] (y: expert-sorted rows of a grouped GEMM), plus
  * gate[t] * shared[t] when shared ([tokens, W], y's dtype) is given (gate fp32 [tokens] or NULL = 1). */
 int b200_moe_combine(const void* y, const long long* dest, const float* p, const void* shared, const float* gate, float* out,
@@ -565,23 +573,50 @@ int b200_multimap_attn_mma(const void* q, const void* ck, const void* cv, const 
                            int max_blocks, void* out, int H, int G, int M, int D, int Dv, int block_size, float scale, int window,
                            int keep_first, int combine, float lambda, float post, float eps, int dtype, void* stream);
 
+/* ---- talking-heads attention over the paged key cache (csrc/talking_attn.cu): raw_g = scale q_g . k - r1[g] log(1 + r2[g]
+ * (i - j)); s_h = sum_g talk[h, g] raw_g; softmax over the last `window` positions (0: all); out_h = sum_j p_h k_j, times
+ * sigmoid(gate) when gate != NULL. Keys are the values: ck [blocks, G, block_size, D]; r1, r2 fp32 [H]; talk fp32 [H, H]. ---- */
+int b200_talking_attn(const void* q, long long ldq, const void* gate, long long ldg, const void* ck, const int* table,
+                      int max_blocks, const int* pos, const int* slot, const float* r1, const float* r2, const float* talk,
+                      void* out, int tokens, int H, int G, int D, int block_size, float scale, int window, int dtype,
+                      void* stream);
+
 /* ---- recurrent mixers of the ragged step (csrc/linear_scan.cu); runs int32 [n_runs, 4] = (first row, rows, first position,
  * state row) or NULL (every token its own run, from pos / slot). A run at position 0 starts from zero state. ---- */
 int b200_short_conv(const float* x, long long ldx, const float* w, const float* state, const int* pos, const int* slot, float* y,
                     long long ldy, int tokens, int C, int taps, int act, void* stream);
+/* The same with a bias per channel (or NULL), `residual` 1: y = x + act(conv(x) + bias), and y in y_dtype (fp32 / bf16). */
+int b200_short_conv_ex(const float* x, long long ldx, const float* w, const float* bias, const float* state, const int* pos,
+                       const int* slot, void* y, long long ldy, int tokens, int C, int taps, int act, int residual, int y_dtype,
+                       void* stream);
 int b200_silu_rows(float* x, long long ld, long long rows, int cols, void* stream);
 int b200_short_conv_tail(const float* x, long long ldx, float* state, const int* runs, const int* pos, const int* slot, int n_runs,
                          int C, int taps, void* stream);
 int b200_delta_gates(float* q, long long ldq, float* k, long long ldk, float* a, long long lda, float* b, long long ldb,
                      const float* dt_bias, const float* A_log, int tokens, int G, int H, int D, float qscale, float unit_eps,
                      void* stream);
-/* mode 0: S <- decay[h] S + k v^T; mode 1: S <- diag(g) S, u = beta (v - S^T k), S <- S + k u^T; o = S^T q (fp32
- * [tokens, H, Dv]). q / k have G heads of D (head h reads h / (H / G)), v H heads of Dv, g [tokens, H * D], beta [tokens, H].
- * act 1: silu on q, k, v as they are read. state fp32 [rows, H, D, Dv]. */
+/* mode 0: S <- decay[h] S + k v^T; mode 1: S <- diag(g) S, u = beta (v - S^T k), S <- S + k u^T; mode 2: S <- a S + b k v^T
+ * with one a and b per token and head (g = a [tokens, H], beta = b [tokens, H]); o = S^T q (fp32 [tokens, H, Dv]). q / k have G
+ * heads of D (head h reads h / (H / G)), v H heads of Dv - ones, g [tokens, H * D] in mode 1, beta [tokens, H]. act 1: silu on q,
+ * k, v as they are read. ones 1: a column of ones is appended to every head of v (Dv counts it). state fp32 [rows, H, D, Dv]. */
 int b200_linear_scan(const float* q, long long ldq, const float* k, long long ldk, const float* v, long long ldv, const float* g,
                      long long ldg, const float* beta, long long ldb, const float* decay, float* state, const int* runs,
                      const int* pos, const int* slot, int n_runs, float* o, int H, int G, int D, int Dv, int mode, int act,
-                     void* stream);
+                     int ones, void* stream);
+/* Capped log gates of an mLSTM and their running maximum (mstate fp32 [rows, H]): a = exp(f + m - m'), b = exp(i - m'),
+ * e = exp(-m'), all fp32 [tokens, H]; gi / gf fp32 rows of stride ldi / ldf holding one column per head. */
+int b200_mlstm_gates(const float* gi, long long ldi, const float* gf, long long ldf, const float* bi, const float* bf, float cap,
+                     float* mstate, const int* runs, const int* pos, const int* slot, int n_runs, int H, float* a, float* b,
+                     float* e, void* stream);
+/* dt = softplus(dt + dt_bias[h]); a = exp(-exp(A_log[h]) dt); b = dt; fp32 [tokens, H]. */
+int b200_ssm_gates(const float* dt, long long ld, const float* dt_bias, const float* A_log, float* a, float* b, long long tokens,
+                   int H, void* stream);
+/* Per token: v = o[h, d] * oscale; e != NULL: v /= max(|o[h, Dv] * oscale|, e[t, h]) + den_eps; skip != NULL: v += skip[h] x[c];
+ * pre != NULL: v *= silu(pre[c]); RMS norm over `groups` equal column groups; times w (w_full 1: [H * Dv], 0: [group size]);
+ * post != NULL: v *= sigmoid(post[c]). o fp32 [tokens, H, ocols]; out [tokens, H * Dv] in out_dtype. */
+int b200_scan_readout(const float* o, int ocols, const float* e, float den_eps, float oscale, const float* skip, const float* x,
+                      long long ldx, const float* pre, long long ldpre, const float* post, long long ldpost, const float* w,
+                      int w_full, void* out, long long tokens, int H, int Dv, int groups, float eps, int out_dtype, void* stream);
 
 #ifdef __cplusplus
 }

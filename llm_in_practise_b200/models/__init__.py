@@ -21,6 +21,11 @@ def _load_duratar(path, dtype, device):
     return duratar_from_pretrained(path, dtype=dtype, device=device)
 
 
+def _load_kudonex(path, dtype, device):
+    from .kudonex import kudonex_from_pretrained
+    return kudonex_from_pretrained(path, dtype=dtype, device=device)
+
+
 # ``architecture`` (or HF ``model_type`` / ``architectures[0]``) of config.json -> loader(path, dtype, device).
 # Anything not listed is read as a Qwen2/Qwen3-style HF checkpoint by ``io.hf.from_pretrained``.
 MODEL_REGISTRY: Dict[str, Callable] = {
@@ -30,6 +35,8 @@ MODEL_REGISTRY: Dict[str, Callable] = {
     "segorax": _load_segorax,
     "Duratar": _load_duratar,
     "duratar": _load_duratar,
+    "Kudonex": _load_kudonex,
+    "kudonex": _load_kudonex,
 }
 
 

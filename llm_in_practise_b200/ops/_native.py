@@ -28,8 +28,16 @@ _ERRORS = {
 }
 
 
+ERR_UNSUPPORTED = 10006
+
+
 class NativeError(RuntimeError):
     pass
+
+
+def has(name: str) -> bool:
+    """True when the loaded library exports ``name`` (a library linked from a subset of the kernel sources lacks some)."""
+    return hasattr(lib(), name)
 
 
 def dtype_code(dt: torch.dtype) -> int:

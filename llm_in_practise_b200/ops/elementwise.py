@@ -338,6 +338,29 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, pos_table: Optional[torch.
     return out
 
 
+def sinusoid_table(n: int, width: int, device, base: float = 10000.0) -> torch.Tensor:
+    """fp32 [n, width] additive position table, formed in float64: column 2i = sin(p w_i), column 2i + 1 = cos(p w_i) with
+    w_i = base^(-2i / width) (the interleaved layout; an odd last column is a sine)."""
+    i2 = torch.arange(0, width, 2, dtype=torch.float64)
+    ang = torch.arange(n, dtype=torch.float64)[:, None] * torch.pow(torch.tensor(base, dtype=torch.float64), -i2 / width)[None, :]
+    tab = torch.stack([ang.sin(), ang.cos()], -1).reshape(n, -1)[:, :width]
+    return tab.to(torch.float32).contiguous().to(device)
+
+
+def embedding_pos(ids: torch.Tensor, table: torch.Tensor, scale: float, pos: torch.Tensor, pos_table: torch.Tensor) -> torch.Tensor:
+    """fp32 [T, W] = ``table[ids] * scale + pos_table[pos]``: embedding rows entering an fp32 stream, every token with its own
+    position (``pos`` int32 [T], ``pos_table`` fp32 [positions, W])."""
+    T, W = ids.shape[0], table.shape[1]
+    if nv.use_native(table):
+        out = torch.empty(T, W, dtype=torch.float32, device=table.device)
+        fn = nv.proto("b200_embedding_pos", [vp, vp, f32, vp, vp, vp, i64, i32, i32, vp])
+        nv.check(fn(nv.ptr(ids), nv.ptr(table), float(scale), nv.ptr(pos), nv.ptr(pos_table), nv.ptr(out), T, W,
+                    nv.dtype_code(table.dtype), nv.stream()), "embedding_pos")
+        nv.count_launch()
+        return out
+    return table[ids].float() * scale + pos_table[pos.long()]
+
+
 # ------------------------------------------------------------------------------------------------
 # clamped gated unit, logit soft cap
 # ------------------------------------------------------------------------------------------------

@@ -199,9 +199,10 @@ def route_topk(h: torch.Tensor, w_router: torch.Tensor, bias: Optional[torch.Ten
     return ti, (tv / tv.sum(-1, keepdim=True) if mode == ROUTE_SOFTMAX_ALL_RENORM else tv)
 
 
-def route_sigmoid_grouped(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], top: int, groups: int = 1,
-                          keep: int = 1, group_top: int = 2, renorm: bool = False, gate_rows: int = 0):
-    """Sigmoid router with a group-limited choice, in fp32 (``b200_moe_route_grouped``). Scores ``s = sigmoid(h W_r^T)``; the
+def route_grouped(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], top: int, groups: int = 1,
+                  keep: int = 1, group_top: int = 2, renorm: bool = False, gate_rows: int = 0, softmax: bool = False):
+    """Router with a group-limited choice, in fp32 (``b200_moe_route_grouped``). Scores ``s = sigmoid(h W_r^T)``, or with
+    ``softmax`` the softmax of the experts' logits over all experts; the
     choice is made on ``s + correction`` (a per-expert offset that steers the load without entering the weights), and only
     among the experts of the ``keep`` groups — ``groups`` equal runs of neighbouring experts — whose ``group_top`` largest
     choice scores sum highest (the other groups' choice scores count as minus infinity). Returns the chosen experts (long
@@ -216,14 +217,16 @@ def route_sigmoid_grouped(h: torch.Tensor, w_router: torch.Tensor, correction: O
         top_p = torch.empty(T, top, dtype=torch.float32, device=h.device)
         gate = torch.empty(T, gate_rows, dtype=torch.float32, device=h.device) if gate_rows else None
         vp, i32, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
-        fn = nv.proto("b200_moe_route_grouped", [vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp])
+        fn = nv.proto("b200_moe_route_grouped", [vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp])
         nv.check(fn(nv.ptr(h), nv.ptr(w_router), nv.ptr(correction), nv.ptr(top_i), nv.ptr(top_p), nv.ptr(gate), T, W, E, gate_rows, top,
-                    groups, keep, group_top, int(renorm), nv.dtype_code(h.dtype), nv.dtype_code(w_router.dtype), nv.stream()),
+                    groups, keep, group_top, int(renorm), int(softmax), nv.dtype_code(h.dtype), nv.dtype_code(w_router.dtype),
+                    nv.stream()),
                  "moe_route_grouped")
         nv.count_launch()
         return top_i, top_p, gate
-    s_all = torch.sigmoid(h.float() @ w_router.float().t())
-    s, gate = s_all[:, :E], (s_all[:, E:].contiguous() if gate_rows else None)
+    z_all = h.float() @ w_router.float().t()
+    s = torch.softmax(z_all[:, :E], -1) if softmax else torch.sigmoid(z_all[:, :E])
+    gate = torch.sigmoid(z_all[:, E:]).contiguous() if gate_rows else None
     choice = s + correction.float() if correction is not None else s.clone()
     if keep < groups:
         per = E // groups
@@ -236,6 +239,9 @@ def route_sigmoid_grouped(h: torch.Tensor, w_router: torch.Tensor, correction: O
     if renorm:
         top_p = top_p / top_p.sum(-1, keepdim=True)
     return top_i, top_p, gate
+
+
+route_sigmoid_grouped = route_grouped          # the name its first user (a sigmoid router) imports
 
 
 def moe_combine(y: torch.Tensor, dest: torch.Tensor, top_p: torch.Tensor, shared: Optional[torch.Tensor] = None,

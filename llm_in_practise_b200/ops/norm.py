@@ -155,13 +155,15 @@ class LayerNorm(torch.nn.Module):
 def sandwich_norm(y: Optional[torch.Tensor], post_w: Optional[torch.Tensor], residual: Optional[torch.Tensor],
                   next_w: Optional[torch.Tensor], eps: float, weight_offset: float = 1.0,
                   out_dtype: Optional[torch.dtype] = None, branch_mult: float = 1.0,
-                  cast_next: bool = False) -> Tuple[Optional[torch.Tensor], torch.Tensor]:
+                  cast_next: bool = False, center: bool = False) -> Tuple[Optional[torch.Tensor], torch.Tensor]:
     """Post-sublayer norm, residual add and the next pre-sublayer norm in one pass over a 32-bit residual stream
     (``b200_sandwich_norm``): ``x = residual + branch_mult * rms(y) * (offset + post_w)``; ``h = rms(x) * (offset + next_w)``.
     ``post_w`` None: ``branch_mult * y`` is added as it is (the embedding entering the stream); ``residual`` None: the stream
     starts at zero; ``next_w`` None: no ``h`` (nothing follows), or with ``cast_next`` ``h`` is ``x`` itself in ``out_dtype``
     (designs whose sublayers read the stream un-normed). Gains are stored as a difference from ``weight_offset`` (1 for
-    zero-centred gains, 0 for plain ones). Returns ``(h, x)`` with ``x`` fp32 and ``h`` in ``out_dtype`` (default: y's)."""
+    zero-centred gains, 0 for plain ones). ``center``: both norms are layer norms without a bias (the row's mean is taken
+    off and the root of the variance divides) instead of RMS norms. Returns ``(h, x)`` with ``x`` fp32 and ``h`` in
+    ``out_dtype`` (default: y's)."""
     src = y if y is not None else residual
     rows, cols = src.shape
     out_dtype = out_dtype or src.dtype
@@ -174,21 +176,27 @@ def sandwich_norm(y: Optional[torch.Tensor], post_w: Optional[torch.Tensor], res
         h = torch.empty(rows, cols, dtype=out_dtype, device=src.device) if (next_w is not None or cast_only) else None
         if y is not None:
             y = y.contiguous()
-        fn = nv.proto("b200_sandwich_norm", [vp, vp, vp, vp, vp, vp, i64, i32, f32, f32, f32, i32, i32, i32, vp])
+        fn = nv.proto("b200_sandwich_norm_c", [vp, vp, vp, vp, vp, vp, i64, i32, f32, f32, f32, i32, i32, i32, i32, vp])
         nv.check(fn(nv.ptr(y), nv.ptr(post_w), nv.ptr(residual), nv.ptr(x), nv.ptr(next_w), nv.ptr(h), rows, cols, eps,
-                    weight_offset, branch_mult, nv.dtype_code(y.dtype if y is not None else torch.float32), nv.dtype_code(out_dtype),
+                    weight_offset, branch_mult, int(center), nv.dtype_code(y.dtype if y is not None else torch.float32),
+                    nv.dtype_code(out_dtype),
                     nv.dtype_code(w_any.dtype if w_any is not None else torch.float32), nv.stream()), "sandwich_norm")
         nv.count_launch()
         return (x if (h is None and cast_next and next_w is None) else h), x
+    def unit(v):
+        if center:
+            v = v - v.mean(-1, keepdim=True)
+        return v / torch.sqrt(v.pow(2).mean(-1, keepdim=True) + eps)
+
     x = torch.zeros(rows, cols, dtype=torch.float32, device=src.device) if residual is None else residual.float()
     if y is not None:
         yf = y.float()
         if post_w is not None:
-            yf = yf / torch.sqrt(yf.pow(2).mean(-1, keepdim=True) + eps) * (weight_offset + post_w.float())
+            yf = unit(yf) * (weight_offset + post_w.float())
         x = x + (yf * branch_mult if branch_mult != 1.0 else yf)
     h = None
     if next_w is not None:
-        h = (x / torch.sqrt(x.pow(2).mean(-1, keepdim=True) + eps) * (weight_offset + next_w.float())).to(out_dtype)
+        h = (unit(x) * (weight_offset + next_w.float())).to(out_dtype)
     elif cast_next:
         h = x.to(out_dtype)
     return h, x

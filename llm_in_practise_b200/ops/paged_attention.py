@@ -42,7 +42,8 @@ def rope_paged_store(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, po
     """Rotate the q and k heads of ``qkv`` [T, (H + Hkv (+ Hkv)) * D] in place (first ``rot_dims`` dims of each head, tables
     ``cos`` / ``sin`` [max_pos, rot_dims / 2] fp32 indexed by ``pos`` int32 [T]) and store token t's keys / values at position
     ``pos[t]`` of cache row ``slot[t]`` (int32 [T]; caches [blocks, Hkv, block_size, D], ``table`` int32 [rows, max_blocks]).
-    With ``v_from_k`` the values are the keys as projected, before rotation, and ``qkv`` has no v section. Returns ``qkv``."""
+    With ``v_from_k`` the values are the keys as projected, before rotation, and ``qkv`` has no v section; ``cache_v`` None:
+    the layer keeps no value pool (its key rows are read as values). Returns ``qkv``."""
     T = qkv.shape[0]
     H, G, D = n_heads, n_kv_heads, head_dim
     rot = D if rot_dims is None else rot_dims
@@ -62,9 +63,11 @@ def rope_paged_store(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, po
     blk = table[sl, pl // BS].long()
     off = pl % BS
     cache_k[blk, :, off] = r[:, H:].to(cache_k.dtype)
-    cache_v[blk, :, off] = (x[:, H:].to(cache_v.dtype) if v_from_k
-                            else qkv[:, (H + G) * D:(H + 2 * G) * D].view(T, G, D).to(cache_v.dtype))
-    qkv[:, :(H + G) * D] = r.reshape(T, (H + G) * D).to(qkv.dtype)
+    if cache_v is not None:
+        cache_v[blk, :, off] = (x[:, H:].to(cache_v.dtype) if v_from_k
+                                else qkv[:, (H + G) * D:(H + 2 * G) * D].view(T, G, D).to(cache_v.dtype))
+    if rot > 0:
+        qkv[:, :(H + G) * D] = r.reshape(T, (H + G) * D).to(qkv.dtype)
     return qkv
 
 

@@ -25,6 +25,7 @@ NATIVE_SOURCES = {
     "Segorax": ["gemm_tcgen05", "gemv", "gemm_simt", "norm", "elementwise", "latent_attn", "moe"],
     "Duratar": ["gemm_tcgen05", "gemv", "gemm_simt", "elementwise", "hyper_conn", "multimap_attn", "multimap_attn_mma",
                 "linear_scan"],
+    "Kudonex": ["gemm_tcgen05", "gemv", "gemm_simt", "norm", "elementwise", "paged_attn", "moe", "linear_scan", "talking_attn"],
 }
 BLOCK = 64
 MAX_LIVE = 4
