@@ -40,6 +40,16 @@ class Pieces:
                 and window == 0 and os.environ.get("B200_PAGED_MMA", "1") != "0")
 
 
+def make_pieces(runs: Sequence[Sequence[int]], device) -> Pieces:
+    """``Pieces`` of a step from its runs ``(first row, rows, position of the first row, cache row)``: every run whole (for
+    the recurrent mixers) and cut into tiles of at most ``TILE_Q`` rows (for the tensor-core attention kernels)."""
+    runs = [[int(v) for v in r] for r in runs if r[1] > 0]
+    tiles = [[first + q0, min(TILE_Q, n - q0), p0 + q0, row] for first, n, p0, row in runs for q0 in range(0, n, TILE_Q)]
+    tl = torch.tensor(tiles + runs, dtype=torch.int32)
+    tl = tl.pin_memory().to(device, non_blocking=True) if torch.device(device).type == "cuda" else tl
+    return Pieces(tl[:len(tiles)], len(tiles), max((r[1] for r in runs), default=0), tl[len(tiles):], len(runs))
+
+
 Entry = Tuple[int, int, Sequence[int], Sequence[int]]       # (cache row, first position, tokens, wanted indices into tokens)
 
 
@@ -101,9 +111,8 @@ class RaggedGenerator(Generator):
         pos: List[int] = []
         slot: List[int] = []
         want: List[int] = []
-        tiles: List[List[int]] = []
         runs: List[List[int]] = []
-        longest = max_pos = 0
+        max_pos = 0
         for row, pos0, toks, wanted in entries:
             n = len(toks)
             if n == 0:
@@ -116,9 +125,6 @@ class RaggedGenerator(Generator):
             slot.extend([row] * n)
             want.extend(base + int(w) for w in wanted)
             runs.append([base, n, pos0, row])
-            for q0 in range(0, n, TILE_Q):
-                tiles.append([base + q0, min(TILE_Q, n - q0), pos0 + q0, row])
-            longest = max(longest, n)
             max_pos = max(max_pos, pos0 + n - 1)
         if not ids:
             return None
@@ -126,11 +132,9 @@ class RaggedGenerator(Generator):
         if dev.type == "cuda":
             meta = meta.pin_memory().to(dev, non_blocking=True)
             ids_t = torch.tensor(ids, dtype=torch.long).pin_memory().to(dev, non_blocking=True)
-            tl = torch.tensor(tiles + runs, dtype=torch.int32).pin_memory().to(dev, non_blocking=True)
         else:
             ids_t = torch.tensor(ids, dtype=torch.long)
-            tl = torch.tensor(tiles + runs, dtype=torch.int32)
-        pieces = Pieces(tl[:len(tiles)], len(tiles), longest, tl[len(tiles):], len(runs))
+        pieces = make_pieces(runs, dev)
         want_t = torch.tensor(want, dtype=torch.long, device=dev) if want else torch.zeros(1, dtype=torch.long, device=dev)
         logits = self.model.forward_ragged(ids_t, meta[0], meta[1], cache, want_t, max_pos=max_pos, pieces=pieces,
                                            layer_outputs=layer_outputs)

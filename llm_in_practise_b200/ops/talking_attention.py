@@ -41,12 +41,14 @@ def talking_attention(q: torch.Tensor, cache_k: torch.Tensor, table: torch.Tenso
         if q.stride(1) != 1 or (gate is not None and gate.stride(1) != 1) or cache_k.dtype != q.dtype:
             raise ValueError("talking_attention: rows must be contiguous and share the cache dtype")
         out = torch.empty(T, H * D, dtype=q.dtype, device=q.device)
-        if (pieces is not None and pieces.longest >= 8 and q.dtype == torch.bfloat16 and D % 16 == 0 and D <= 128 and H <= 32
-                and window > 0 and nv.has("b200_talking_attn_mma") and os.environ.get("B200_TALKING_MMA", "1") != "0"):
+        if (pieces is not None and pieces.longest >= 8 and q.dtype == torch.bfloat16 and D % 16 == 0 and D <= 128 and H <= 16
+                and nv.has("b200_talking_attn_mma") and os.environ.get("B200_TALKING_MMA", "1") != "0"):
+            # every 64-row tile of the step becomes up to four CTAs of 16 rows; sizes the kernel does not take come back as
+            # "unsupported" and go to the per-token kernel below
             fn = nv.proto("b200_talking_attn_mma", [vp, i64, vp, i64, vp, vp, i32, vp, i32, vp, vp, vp, vp, i32, i32, i32, i32, f32,
                                                     i32, vp])
             rc = fn(nv.ptr(q), q.stride(0), nv.ptr(gate), gate.stride(0) if gate is not None else 0, nv.ptr(cache_k),
-                    nv.ptr(pieces.tiles16), pieces.n_tiles16, nv.ptr(table), table.shape[1], nv.ptr(r1), nv.ptr(r2), nv.ptr(talk),
+                    nv.ptr(pieces.tiles), pieces.n_tiles, nv.ptr(table), table.shape[1], nv.ptr(r1), nv.ptr(r2), nv.ptr(talk),
                     nv.ptr(out), H, G, D, BS, float(scale), int(window), nv.stream())
             if rc == 0:
                 nv.count_launch()

@@ -25,7 +25,8 @@ NATIVE_SOURCES = {
     "Segorax": ["gemm_tcgen05", "gemv", "gemm_simt", "norm", "elementwise", "latent_attn", "moe"],
     "Duratar": ["gemm_tcgen05", "gemv", "gemm_simt", "elementwise", "hyper_conn", "multimap_attn", "multimap_attn_mma",
                 "linear_scan"],
-    "Kudonex": ["gemm_tcgen05", "gemv", "gemm_simt", "norm", "elementwise", "paged_attn", "moe", "linear_scan", "talking_attn"],
+    "Kudonex": ["gemm_tcgen05", "gemv", "gemm_simt", "norm", "elementwise", "paged_attn", "moe", "linear_scan", "talking_attn",
+                "talking_attn_mma"],
 }
 BLOCK = 64
 MAX_LIVE = 4

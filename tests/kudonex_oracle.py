@@ -117,9 +117,9 @@ def attention(h, P, m):
     for i in range(n):
         lo = max(0, i - win + 1)
         raw = torch.zeros(H, i + 1 - lo, dtype=F64)
+        dist = torch.arange(i - lo, -1, -1, dtype=F64)                            # i - j for j = lo .. i
         for a in range(H):
-            for j in range(lo, i + 1):
-                raw[a, j - lo] = float(q[i, a] @ k[j, a // (H // G)]) * scale - float(r1[a]) * math.log1p(float(r2[a]) * (i - j))
+            raw[a] = (k[lo:i + 1, a // (H // G)] @ q[i, a]) * scale - r1[a] * torch.log1p(r2[a] * dist)
         p = torch.softmax(T @ raw, -1)
         for a in range(H):
             ctx[i, a] = p[a] @ k[lo:i + 1, a // (H // G)]
@@ -154,7 +154,7 @@ def moe(h, P, f):
     for t in range(h.shape[0]):
         for e, w in zip(chosen[t], weights[t]):
             out[t] += w * expert(h[t:t + 1], P, f"e{e}.")[0]
-    return out + expert(h, P, "shared.")
+    return out + expert(h, P, "shared.") if "shared.gate" in P else out
 
 
 def sub(weights, prefix):
@@ -180,3 +180,85 @@ def forward(cfg, weights, tokens):
             x = x + layer_norm(moe(h, sub(weights, p + "mlp."), L["mlp"]), weights[p + "norm2b"], eps)
         streams.append(x.clone())
     return layer_norm(x, weights["final.norm"], eps) @ weights["embed"].to(F64).t(), streams
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# small random models for the tests
+# ------------------------------------------------------------------------------------------------------------------
+def moe_spec(experts, top, ff, groups=1, keep=1, shared=0):
+    return {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top, "groups": {"count": groups, "keep": keep}},
+            "shared": {"ff": shared}}
+
+
+def mlstm_layer(heads, dim, vdim, cap=15.0, mlp=None):
+    return {"type": "mlstm", "mixer": {"heads": heads, "dim": dim, "vdim": vdim, "gate_cap": cap}, "mlp": mlp}
+
+
+def mamba2_layer(heads, vdim, state, groups=1, norm_groups=1, conv=4, mlp=None):
+    return {"type": "mamba2", "mixer": {"heads": heads, "vdim": vdim, "state": state, "groups": groups, "norm_groups": norm_groups,
+                                        "conv": conv}, "mlp": mlp}
+
+
+def attention_layer(heads, kv_heads, dim, window, scale=None, mlp=None):
+    return {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "mask": {"size": window},
+                                           "scale": dim ** -0.5 if scale is None else scale}, "mlp": mlp}
+
+
+def make_config(width, vocab, layers, taps=4, embed_scale=3.0, eps=1e-5):
+    return {"architecture": "Kudonex", "vocab": vocab, "width": width, "norm": {"eps": eps}, "embedding": {"scale": embed_scale},
+            "canon": {"taps": taps}, "layers": layers}
+
+
+def random_weights(cfg, seed=0):
+    """bf16 tensors under the checkpoint's names; scales chosen so that every mechanism matters (gates away from saturation,
+    distance penalties and head mixing of the order of the scores, corrections that change which experts are chosen)."""
+    g = torch.Generator().manual_seed(seed)
+    W = cfg["width"]
+    out = {}
+    rnd = lambda *s, std=1.0: torch.randn(*s, generator=g) * std                       # noqa: E731
+    lin = lambda o, i, gain=1.0: rnd(o, i, std=gain * i ** -0.5)                        # noqa: E731
+    gain = lambda n: 1.0 + rnd(n, std=0.2)                                             # noqa: E731
+    out["embed"] = rnd(cfg["vocab"], W, std=0.5)
+    out["final.norm"] = gain(W)
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        for n in ("norm1", "norm1b"):
+            out[p + n] = gain(W)
+        out[p + "canon1"] = rnd(W, cfg["canon"]["taps"], std=0.4)
+        H, Dv = m["heads"], m["vdim"]
+        if L["type"] == "mlstm":
+            D = m["dim"]
+            out.update({p + "mix.q": lin(H * D, W, 2.0), p + "mix.k": lin(H * D, W, 2.0), p + "mix.v": lin(H * Dv, W), p + "mix.g": lin(H * Dv, W),
+                        p + "mix.i": lin(H, W, 3.0), p + "mix.f": lin(H, W, 3.0), p + "mix.i.b": rnd(H), p + "mix.f.b": rnd(H) + 2.0,
+                        p + "mix.norm": gain(H * Dv), p + "mix.o": lin(W, H * Dv)})
+        elif L["type"] == "mamba2":
+            N, G = m["state"], m["groups"]
+            C = H * Dv + 2 * G * N
+            out.update({p + "mix.in": lin(2 * H * Dv + 2 * G * N + H, W, 1.5), p + "mix.conv": rnd(C, m["conv"], std=0.5),
+                        p + "mix.conv.b": rnd(C, std=0.3), p + "mix.dt_bias": rnd(H) - 1.0, p + "mix.A_log": rnd(H, std=0.5),
+                        p + "mix.D": rnd(H), p + "mix.norm": gain(H * Dv), p + "mix.o": lin(W, H * Dv)})
+        else:
+            D, G = m["dim"], m["kv_heads"]
+            out.update({p + "mix.q": lin(H * D, W, 2.0), p + "mix.k": lin(G * D, W, 2.0), p + "mix.g": lin(H * D, W), p + "mix.o": lin(W, H * D),
+                        p + "mix.r1": torch.rand(H, generator=g) * 1.5, p + "mix.r2": torch.rand(H, generator=g) * 2.0 + 0.05,
+                        p + "mix.talk": torch.eye(H) + rnd(H, H, std=0.3)})
+        f = L.get("mlp")
+        if f is None:
+            continue
+        for n in ("norm2", "norm2b"):
+            out[p + n] = gain(W)
+        E, F, Fs = f["router"]["experts"], f["expert"]["ff"], f["shared"]["ff"]
+        out[p + "mlp.router"] = lin(E, W, 2.0)
+        out[p + "mlp.correction"] = rnd(E, std=0.3) - 0.2
+        for e in range(E):
+            out.update({f"{p}mlp.e{e}.gate": lin(F, W), f"{p}mlp.e{e}.up": lin(F, W), f"{p}mlp.e{e}.down": lin(W, F)})
+        if Fs:
+            out.update({p + "mlp.shared.gate": lin(Fs, W), p + "mlp.shared.up": lin(Fs, W), p + "mlp.shared.down": lin(W, Fs)})
+    return {k: v.to(torch.bfloat16).contiguous() for k, v in out.items()}
+
+
+def greedy(cfg, weights, prompt, new):
+    toks = list(prompt)
+    for _ in range(new):
+        toks.append(int(forward(cfg, weights, toks)[0][-1].argmax()))
+    return toks
