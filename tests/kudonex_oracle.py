@@ -248,10 +248,13 @@ def random_weights(cfg, seed=0):
         for n in ("norm2", "norm2b"):
             out[p + n] = gain(W)
         E, F, Fs = f["router"]["experts"], f["expert"]["ff"], f["shared"]["ff"]
-        out[p + "mlp.router"] = lin(E, W, 2.0)
-        out[p + "mlp.correction"] = rnd(E, std=0.3) - 0.2
+        # a peaked router: the experts that carry weight win by a margin that 16-bit rounding of h does not close, and
+        # the ones decided by a hair carry little; beside a shared expert the routed ones are the smaller part of the sum, so
+        # that a choice that falls the other way in 16 bits does not swamp the recurrent states after it
+        out[p + "mlp.router"] = lin(E, W, 12.0)
+        out[p + "mlp.correction"] = rnd(E, std=0.15) - 0.1
         for e in range(E):
-            out.update({f"{p}mlp.e{e}.gate": lin(F, W), f"{p}mlp.e{e}.up": lin(F, W), f"{p}mlp.e{e}.down": lin(W, F)})
+            out.update({f"{p}mlp.e{e}.gate": lin(F, W), f"{p}mlp.e{e}.up": lin(F, W), f"{p}mlp.e{e}.down": lin(W, F, 0.3 if Fs else 1.0)})
         if Fs:
             out.update({p + "mlp.shared.gate": lin(Fs, W), p + "mlp.shared.up": lin(Fs, W), p + "mlp.shared.down": lin(W, Fs)})
     return {k: v.to(torch.bfloat16).contiguous() for k, v in out.items()}

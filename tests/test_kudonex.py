@@ -476,8 +476,8 @@ def test_whole_prompt_and_residuals(tmp_path, device, dtype, variant):
     for i, L in enumerate(cfg["layers"]):                        # only attention layers hold pages, and no value pool
         assert (cache.k[i].numel() > 0) == (L["type"] == "attention") and cache.v[i].numel() == 0
         assert len(cache.state[i]) == (1 if L["type"] == "attention" else 3)
-    for a, b in zip(res, res_ref):
-        assert_rows(a, b, dtype, variant)
+    for li, (a, b) in enumerate(zip(res, res_ref)):
+        assert_rows(a, b, dtype, (variant, li))
     assert_rows(got, ref, dtype, variant)
     # the first tokens of a sequence: a one-token request and the start of a longer one agree with the oracle row by row
     one = gen.step([(0, 0, toks[:1], [0])], fresh_cache(gen, 1, 64))
