@@ -46,10 +46,10 @@ def parse_args():
     ap.add_argument("--sequential-accum", action="store_true",
                     help="run the micro-batches one after the other (round-1 schedule) instead of one layer-major pass")
     ap.add_argument("--local_rank", type=int, default=-1)
-    ap.add_argument("--workload", default="headline", choices=["headline", "gorozen", "segorax", "duratar"],
+    ap.add_argument("--workload", default="headline", choices=["headline", "gorozen", "segorax", "duratar", "kudonex"],
                     help="gorozen: prefill / decode throughput and kernel rooflines of the Gorozen design beside Qwen3 at equal "
-                         "layer sizes (one GPU, serving path); segorax / duratar: the same for those designs beside Gorozen; the "
-                         "default is the headline training step")
+                         "layer sizes (one GPU, serving path); segorax / duratar: the same for those designs beside Gorozen; "
+                         "kudonex: the same beside Duratar; the default is the headline training step")
     return ap.parse_args()
 
 
@@ -143,6 +143,10 @@ def main():
         sys.path.insert(0, os.path.join(ROOT, "bench"))
         import duratar_bench
         return duratar_bench.run(args, ROOT)
+    if args.workload == "kudonex":
+        sys.path.insert(0, os.path.join(ROOT, "bench"))
+        import kudonex_bench
+        return kudonex_bench.run(args, ROOT)
 
     import torch
     import torch.distributed as dist

@@ -581,11 +581,11 @@ int b200_talking_attn(const void* q, long long ldq, const void* gate, long long 
                       void* out, int tokens, int H, int G, int D, int block_size, float scale, int window, int dtype,
                       void* stream);
 
-/* The same for bf16 prompt pieces on mma.sync: tiles int32 [n_tiles, 4] = (first row, rows <= 64, position of the first row,
- * cache row), each cut into CTAs of 16 rows that own all heads. H <= 16, D in {16, 32, 48, 64, 96, 128}, q rows on 16-byte
- * boundaries; else B200_ERR_UNSUPPORTED (use b200_talking_attn). */
+/* The same for bf16 on mma.sync: tiles int32 [n_tiles, 4] = (first row, rows <= 64, position of the first row, cache row), each
+ * cut into CTAs of 16 rows that own all heads; tiles NULL: n_tiles single tokens with pos / slot read on the device. H <= 16,
+ * D in {16, 32, 48, 64, 96, 128}, q rows on 16-byte boundaries; else B200_ERR_UNSUPPORTED (use b200_talking_attn). */
 int b200_talking_attn_mma(const void* q, long long ldq, const void* gate, long long ldg, const void* ck, const int* tiles,
-                          int n_tiles, const int* table, int max_blocks, const float* r1, const float* r2, const float* talk,
+                          int n_tiles, const int* pos, const int* slot, const int* table, int max_blocks, const float* r1, const float* r2, const float* talk,
                           void* out, int H, int G, int D, int block_size, float scale, int window, void* stream);
 
 /* ---- recurrent mixers of the ragged step (csrc/linear_scan.cu); runs int32 [n_runs, 4] = (first row, rows, first position,

@@ -33,7 +33,9 @@ def talking_attention(q: torch.Tensor, cache_k: torch.Tensor, table: torch.Tenso
     """Context [T, H * D] in q's dtype. ``q`` [T, >= H * D] (query heads first; rows may be strided: a slice of a fused
     projection), ``gate`` [T, H * D] or None (same dtype, rows may be strided), ``cache_k`` [blocks, G, block_size, D],
     ``r1`` / ``r2`` fp32 [H], ``talk`` fp32 [H, H] indexed [to, from]. ``window`` 0: every earlier key is visible.
-    ``pieces``: optional ``Pieces`` of the step; 16-bit prompt pieces then go through the tensor-core kernel."""
+    ``pieces``: optional ``Pieces`` of the step (None: every token stands alone, a decode batch). bf16 runs with at most 16
+    heads of a size the tensor-core kernel takes go through it, pieces and single tokens alike; everything else (fp32 runs,
+    other sizes) through the per-token kernel."""
     T = q.shape[0]
     H, G, D = n_heads, n_kv_heads, head_dim
     BS = cache_k.shape[2]
@@ -41,14 +43,16 @@ def talking_attention(q: torch.Tensor, cache_k: torch.Tensor, table: torch.Tenso
         if q.stride(1) != 1 or (gate is not None and gate.stride(1) != 1) or cache_k.dtype != q.dtype:
             raise ValueError("talking_attention: rows must be contiguous and share the cache dtype")
         out = torch.empty(T, H * D, dtype=q.dtype, device=q.device)
-        if (pieces is not None and pieces.longest >= 8 and q.dtype == torch.bfloat16 and D % 16 == 0 and D <= 128 and H <= 16
-                and nv.has("b200_talking_attn_mma") and os.environ.get("B200_TALKING_MMA", "1") != "0"):
-            # every 64-row tile of the step becomes up to four CTAs of 16 rows; sizes the kernel does not take come back as
-            # "unsupported" and go to the per-token kernel below
-            fn = nv.proto("b200_talking_attn_mma", [vp, i64, vp, i64, vp, vp, i32, vp, i32, vp, vp, vp, vp, i32, i32, i32, i32, f32,
-                                                    i32, vp])
+        if (q.dtype == torch.bfloat16 and D % 16 == 0 and D <= 128 and H <= 16 and nv.has("b200_talking_attn_mma")
+                and os.environ.get("B200_TALKING_MMA", "1") != "0"):
+            # every 64-row tile of the step becomes up to four CTAs of 16 rows, and without pieces (a decode batch) every
+            # token is a tile of one row; sizes the kernel does not take come back as "unsupported" and go to the
+            # per-token kernel below
+            fn = nv.proto("b200_talking_attn_mma", [vp, i64, vp, i64, vp, vp, i32, vp, vp, vp, i32, vp, vp, vp, vp, i32, i32, i32, i32,
+                                                    f32, i32, vp])
+            tiles, n = (pieces.tiles, pieces.n_tiles) if pieces is not None else (None, T)
             rc = fn(nv.ptr(q), q.stride(0), nv.ptr(gate), gate.stride(0) if gate is not None else 0, nv.ptr(cache_k),
-                    nv.ptr(pieces.tiles), pieces.n_tiles, nv.ptr(table), table.shape[1], nv.ptr(r1), nv.ptr(r2), nv.ptr(talk),
+                    nv.ptr(tiles), n, nv.ptr(pos), nv.ptr(slot), nv.ptr(table), table.shape[1], nv.ptr(r1), nv.ptr(r2), nv.ptr(talk),
                     nv.ptr(out), H, G, D, BS, float(scale), int(window), nv.stream())
             if rc == 0:
                 nv.count_launch()
