@@ -356,19 +356,27 @@ mlstm_gates_kernel(const float* __restrict__ gi, long long ldi, const float* __r
   else { first = r; n = 1; p0 = pos[r]; s = slot[r]; }
   float m = p0 > 0 ? mstate[(long long)s * H + h] : 0.f;
   const float bih = bi[h], bfh = bf[h];
+  // the next chunk's gate inputs are fetched while this one is walked
+  float gin = 0.f, gfn = 0.f;
+  if (lane < n) { gin = gi[(long long)(first + lane) * ldi + h]; gfn = gf[(long long)(first + lane) * ldf + h]; }
   for (int c0 = 0; c0 < n; c0 += 32) {
     const int cn = min(32, n - c0);
+    const float gic = gin, gfc = gfn;
+    if (c0 + 32 + lane < n) {
+      gin = gi[(long long)(first + c0 + 32 + lane) * ldi + h];
+      gfn = gf[(long long)(first + c0 + 32 + lane) * ldf + h];
+    }
     float fv = 0.f, iv = 0.f;
     if (lane < cn) {
-      const long long t = first + c0 + lane;
-      iv = cap * tanhf((gi[t * ldi + h] + bih) / cap);
-      const float z = cap * tanhf((gf[t * ldf + h] + bfh) / cap);
+      iv = cap * tanhf((gic + bih) / cap);
+      const float z = cap * tanhf((gfc + bfh) / cap);
       fv = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));        // log sigmoid(z)
     }
     fs[warp][lane] = fv;
     is[warp][lane] = iv;
     __syncwarp();
     float mprev = 0.f, mnew = 0.f;
+#pragma unroll 8
     for (int j = 0; j < cn; ++j) {
       const float nm = fmaxf(fs[warp][j] + m, is[warp][j]);
       if (j == lane) { mprev = m; mnew = nm; }

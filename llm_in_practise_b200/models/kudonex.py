@@ -281,10 +281,12 @@ class KudonexForCausalLM(nn.Module):
         return out
 
     def pos_table(self, device, need: int) -> torch.Tensor:
-        t = self._pos_table.get(str(device))
-        if t is None or t.shape[0] < need:
-            t = self._pos_table[str(device)] = ew.sinusoid_table(max(need, 1024), self.config.hidden_size, device, POS_BASE)
-        return t
+        """The additive position table for at least ``need`` positions. A table that had to grow leaves the old one alive:
+        CUDA graphs captured against a smaller cache still read it."""
+        tabs = self._pos_table.setdefault(str(device), [])
+        if not tabs or tabs[-1].shape[0] < need:
+            tabs.append(ew.sinusoid_table(max(need, 1024), self.config.hidden_size, device, POS_BASE))
+        return tabs[-1]
 
     @torch.no_grad()
     def forward_ragged(self, ids: torch.Tensor, pos: torch.Tensor, slot: torch.Tensor, cache, want: Optional[torch.Tensor] = None,
