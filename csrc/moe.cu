@@ -16,6 +16,64 @@
 
 namespace b200 {
 
+template <typename T> __device__ __forceinline__ void route_load8(const T* p, float (&v)[8]);
+template <> __device__ __forceinline__ void route_load8<float>(const float* p, float (&v)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <> __device__ __forceinline__ void route_load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* q = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(q[i]);
+    v[2 * i] = f.x; v[2 * i + 1] = f.y;
+  }
+}
+
+// z[r] = W_r[r, :] . h for r < rows, by one warp, fp32 accumulation. Rows are taken eight at a time so that eight rows' loads
+// are in flight per lane (a row after the other waits a memory round trip per 32 columns); 16-byte loads where the width
+// and the pointers allow, lane-strided scalar loads otherwise. Lane 0 writes z.
+template <typename TH, typename TW>
+__device__ __forceinline__ void route_logits(const TH* __restrict__ hr, const TW* __restrict__ wr, int W, int rows, int lane,
+                                             float* __restrict__ z) {
+  constexpr int EB = 8;
+  const bool vec = W % 8 == 0 && ((reinterpret_cast<uintptr_t>(hr) | reinterpret_cast<uintptr_t>(wr)) & 15) == 0;
+  for (int e0 = 0; e0 < rows; e0 += EB) {
+    float acc[EB];
+    const TW* wrow[EB];
+#pragma unroll
+    for (int j = 0; j < EB; ++j) {
+      acc[j] = 0.f;
+      wrow[j] = wr + (long long)min(e0 + j, rows - 1) * W;      // rows past the last repeat it: every load is unconditional
+    }
+    if (vec) {
+      for (int c = lane * 8; c < W; c += 256) {
+        float hv[8];
+        route_load8<TH>(hr + c, hv);
+#pragma unroll
+        for (int j = 0; j < EB; ++j) {
+          float wv[8];
+          route_load8<TW>(wrow[j] + c, wv);
+#pragma unroll
+          for (int x = 0; x < 8; ++x) acc[j] = fmaf(hv[x], wv[x], acc[j]);
+        }
+      }
+    } else {
+      for (int i = lane; i < W; i += 32) {
+        const float hv = to_f32<TH>(hr[i]);
+#pragma unroll
+        for (int j = 0; j < EB; ++j) acc[j] = fmaf(hv, to_f32<TW>(wrow[j][i]), acc[j]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < EB; ++j) {
+      const float a = warp_sum(acc[j]);
+      if (lane == 0 && e0 + j < rows) z[e0 + j] = a;
+    }
+  }
+}
+
 template <typename TH, typename TW>
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const TH* __restrict__ h, const TW* __restrict__ wr, const float* __restrict__ bias, long long* __restrict__ top_i,
@@ -26,19 +84,13 @@ moe_route_kernel(const TH* __restrict__ h, const TW* __restrict__ wr, const floa
   if (t >= tokens) return;
   float* z = zbuf + warp * E;
   const TH* hr = h + t * W;
-  for (int e = 0; e < E; ++e) {
-    const TW* w = wr + (long long)e * W;
-    float a = 0.f;
-    for (int i = lane; i < W; i += 32) a = fmaf(to_f32<TH>(hr[i]), to_f32<TW>(w[i]), a);
-    a = warp_sum(a);
-    if (lane == 0) {
-      const float v = a + (bias ? bias[e] : 0.f);
-      z[e] = v;
-      if (logits_out) logits_out[t * E + e] = v;
-    }
-  }
+  route_logits<TH, TW>(hr, wr, W, E, lane, z);
   __syncwarp();
   if (lane != 0) return;
+  for (int e = 0; e < E; ++e) {
+    z[e] += bias ? bias[e] : 0.f;
+    if (logits_out) logits_out[t * E + e] = z[e];
+  }
   float zmax = -INFINITY, zsum = 0.f;
   if (mode != 0) {
     for (int e = 0; e < E; ++e) zmax = fmaxf(zmax, z[e]);
@@ -74,15 +126,10 @@ moe_route_grouped_kernel(const TH* __restrict__ h, const TW* __restrict__ wr, co
   float* choice = s + E + X;
   float* gs = choice + E;
   const TH* hr = h + t * W;
-  for (int e = 0; e < E + X; ++e) {
-    const TW* w = wr + (long long)e * W;
-    float a = 0.f;
-    for (int i = lane; i < W; i += 32) a = fmaf(to_f32<TH>(hr[i]), to_f32<TW>(w[i]), a);
-    a = warp_sum(a);
-    if (lane == 0) s[e] = (softmax && e < E) ? a : 1.f / (1.f + expf(-a));
-  }
+  route_logits<TH, TW>(hr, wr, W, E + X, lane, s);
   __syncwarp();
   if (lane != 0) return;
+  for (int e = softmax ? E : 0; e < E + X; ++e) s[e] = 1.f / (1.f + expf(-s[e]));
   if (softmax) {                                       // scores are the softmax of the logits over all experts
     float zmax = -INFINITY, zsum = 0.f;
     for (int e = 0; e < E; ++e) zmax = fmaxf(zmax, s[e]);

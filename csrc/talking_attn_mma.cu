@@ -40,7 +40,7 @@ talking_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, cons
                         const __nv_bfloat16* __restrict__ ck, const int* __restrict__ tiles, const int* __restrict__ pos,
                         const int* __restrict__ slots, const int* __restrict__ table, int max_blocks, const float* __restrict__ r1,
                         const float* __restrict__ r2, const float* __restrict__ talk, __nv_bfloat16* __restrict__ out, int H, int G,
-                        int bs_log2, float scale, int window, int nbuf) {
+                        int bs_log2, float scale, int window, int nbuf, float* __restrict__ part) {
   constexpr int D = KS * 16;
   constexpr int QR = SINGLE ? 1 : kTmRows;                // rows of the query and score buffers
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -81,6 +81,14 @@ talking_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, cons
   const int* trow = table + (long long)slot * max_blocks;
   const int lo = window > 0 ? max(0, p0 - window + 1) : 0, hi = p0 + nr - 1;
   const int nchunks = (hi - lo) / kTmKeys + 1;
+  // a single token's chunks may be shared out over gridDim.y CTAs (`part` given): each walks a run of chunks and leaves its
+  // unnormalised sums, running maximum and normaliser per head for the merge kernel
+  int k_lo = 0, k_hi = nchunks;
+  if (SINGLE && part) {
+    const int per = (nchunks + (int)gridDim.y - 1) / (int)gridDim.y;
+    k_lo = min(nchunks, sub * per);
+    k_hi = min(nchunks, k_lo + per);
+  }
   // chunk k (k = 0 is the one nearest to the queries: the running maximum settles early and later chunks seldom rescale)
   auto chunk_j0 = [&](int k) { return lo + (nchunks - 1 - k) * kTmKeys; };
 
@@ -105,18 +113,18 @@ talking_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, cons
   for (int nt = 0; nt < 2 * KS; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
-  for (int k = 0; k < nbuf - 1; ++k) {                      // the first chunks are on their way before the walk starts
-    if (k < nchunks) stage(k, chunk_j0(k));
+  for (int k = k_lo; k < k_lo + nbuf - 1; ++k) {            // the first chunks are on their way before the walk starts
+    if (k < k_hi) stage((k - k_lo) % nbuf, chunk_j0(k));
     cp_async_commit();
   }
-  for (int k = 0; k < nchunks; ++k) {
+  for (int k = k_lo; k < k_hi; ++k) {
     const int j0 = chunk_j0(k);
     __syncthreads();                                      // the previous chunk's keys and scores have been used (and Qs is there)
-    if (k + nbuf - 1 < nchunks) stage((k + nbuf - 1) % nbuf, chunk_j0(k + nbuf - 1));
+    if (k + nbuf - 1 < k_hi) stage((k - k_lo + nbuf - 1) % nbuf, chunk_j0(k + nbuf - 1));
     cp_async_commit();
     cp_async_wait_upto<4>(nbuf - 1);
     __syncthreads();
-    const __nv_bfloat16* Ks = Kbuf + (k % nbuf) * kTmKeys * ldks;
+    const __nv_bfloat16* Ks = Kbuf + ((k - k_lo) % nbuf) * kTmKeys * ldks;
     // the penalty depends on the head and on the distance only: the 47 distances a chunk's (row, key) pairs can have are
     // formed once per head here, not once per pair
     for (int x = lane; x < kTmKeys + kTmRows - 1; x += 32) {
@@ -261,6 +269,15 @@ talking_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, cons
       }
     }
   }
+  if (SINGLE && part) {                                     // row 0 lives in the lanes of the first quad row
+    if (rr == 0) {
+      float* dst = part + (((long long)tile * gridDim.y + sub) * H + h) * (D + 2);
+#pragma unroll
+      for (int nt = 0; nt < 2 * KS; ++nt) *reinterpret_cast<float2*>(dst + nt * 8 + 2 * qd) = make_float2(o[nt][0], o[nt][1]);
+      if (qd == 0) *reinterpret_cast<float2*>(dst + D) = make_float2(m0, l0);
+    }
+    return;
+  }
   const float i0 = 1.f / l0, i1 = 1.f / l1;
 #pragma unroll
   for (int nt = 0; nt < 2 * KS; ++nt) {
@@ -280,14 +297,39 @@ talking_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, cons
     }
   }
 }
+
+// out[t, h, :] = sum_s w_s o_s / sum_s w_s l_s, w_s = exp(m_s - max_s m_s), over the S partial walks of a token; then the gate.
+__global__ void __launch_bounds__(256)
+talking_attn_merge_kernel(const float* __restrict__ part, const __nv_bfloat16* __restrict__ gate, long long ldg,
+                          __nv_bfloat16* __restrict__ out, int H, int D, int S) {
+  const long long t = blockIdx.x;
+  for (int idx = threadIdx.x; idx < H * D; idx += blockDim.x) {
+    const int h = idx / D, d = idx - h * D;
+    const float* p = part + ((t * S) * H + h) * (D + 2);
+    const long long ss = (long long)H * (D + 2);
+    float M = -INFINITY;
+    for (int s = 0; s < S; ++s) M = fmaxf(M, p[s * ss + D]);
+    float num = 0.f, den = 0.f;
+    for (int s = 0; s < S; ++s) {
+      const float m = p[s * ss + D];
+      const float w = m == -INFINITY ? 0.f : expf(m - M);
+      num = fmaf(w, p[s * ss + d], num);
+      den = fmaf(w, p[s * ss + D + 1], den);
+    }
+    float v = num / den;
+    if (gate) v *= 1.f / (1.f + expf(-__bfloat162float(gate[t * ldg + idx])));
+    out[t * (long long)(H * D) + idx] = __float2bfloat16(v);
+  }
+}
 }  // namespace b200
 
 B200_API int b200_talking_attn_mma(const void* q, long long ldq, const void* gate, long long ldg, const void* ck, const int* tiles,
                                    int n_tiles, const int* pos, const int* slot, const int* table, int max_blocks,
                                    const float* r1, const float* r2, const float* talk, void* out, int H, int G, int D,
-                                   int block_size, float scale, int window, void* stream) {
+                                   int block_size, float scale, int window, float* part, int nsplit, void* stream) {
   using namespace b200;
   if (n_tiles <= 0) return 0;
+  if (nsplit < 1 || nsplit > 65535 || (nsplit > 1 && (!part || tiles))) return B200_ERR_BAD_SHAPE;
   if (H <= 0 || G <= 0 || H % G || D <= 0 || block_size <= 0 || (block_size & (block_size - 1)) || window < 0)
     return B200_ERR_BAD_SHAPE;
   if (H > kTmMaxHeads || D % 16 || D > 128 || D == 80 || D == 112 || ldq % 8 || (reinterpret_cast<uintptr_t>(q) & 15))
@@ -307,14 +349,15 @@ B200_API int b200_talking_attn_mma(const void* q, long long ldq, const void* gat
   int bs_log2 = 0;
   while ((1 << bs_log2) < block_size) ++bs_log2;
   cudaStream_t st = (cudaStream_t)stream;
-  dim3 grid(n_tiles, single ? 1 : 4);
+  dim3 grid(n_tiles, single ? nsplit : 4);
+  float* pw = nsplit > 1 ? part : nullptr;
   typedef __nv_bfloat16 bf;
 #define TMMA_K(KS, SG)                                                                                                        \
   do {                                                                                                                        \
     auto kern = talking_attn_mma_kernel<KS, SG>;                                                                              \
     if (smem > 48 * 1024) B200_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));     \
     kern<<<grid, H * 32, smem, st>>>((const bf*)q, ldq, (const bf*)gate, ldg, (const bf*)ck, tiles, pos, slot, table, max_blocks, \
-                                     r1, r2, talk, (bf*)out, H, G, bs_log2, scale, window, nbuf);                             \
+                                     r1, r2, talk, (bf*)out, H, G, bs_log2, scale, window, nbuf, pw);                         \
   } while (0)
 #define TMMA(KS)                                                                                                              \
   do {                                                                                                                        \
@@ -331,5 +374,9 @@ B200_API int b200_talking_attn_mma(const void* q, long long ldq, const void* gat
 #undef TMMA
 #undef TMMA_K
   B200_LAUNCH_CHECK();
+  if (pw) {
+    talking_attn_merge_kernel<<<n_tiles, 256, 0, st>>>(pw, (const bf*)gate, ldg, (bf*)out, H, D, nsplit);
+    B200_LAUNCH_CHECK();
+  }
   return 0;
 }

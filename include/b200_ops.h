@@ -583,10 +583,13 @@ int b200_talking_attn(const void* q, long long ldq, const void* gate, long long 
 
 /* The same for bf16 on mma.sync: tiles int32 [n_tiles, 4] = (first row, rows <= 64, position of the first row, cache row), each
  * cut into CTAs of 16 rows that own all heads; tiles NULL: n_tiles single tokens with pos / slot read on the device. H <= 16,
- * D in {16, 32, 48, 64, 96, 128}, q rows on 16-byte boundaries; else B200_ERR_UNSUPPORTED (use b200_talking_attn). */
+ * D in {16, 32, 48, 64, 96, 128}, q rows on 16-byte boundaries; else B200_ERR_UNSUPPORTED (use b200_talking_attn).
+ * nsplit > 1 (single tokens only): every token's keys are walked by nsplit CTAs that leave their partial sums in
+ * part, fp32 [n_tiles, nsplit, H, D + 2], and a second kernel merges them. */
 int b200_talking_attn_mma(const void* q, long long ldq, const void* gate, long long ldg, const void* ck, const int* tiles,
                           int n_tiles, const int* pos, const int* slot, const int* table, int max_blocks, const float* r1, const float* r2, const float* talk,
-                          void* out, int H, int G, int D, int block_size, float scale, int window, void* stream);
+                          void* out, int H, int G, int D, int block_size, float scale, int window, float* part, int nsplit,
+                          void* stream);
 
 /* ---- recurrent mixers of the ragged step (csrc/linear_scan.cu); runs int32 [n_runs, 4] = (first row, rows, first position,
  * state row) or NULL (every token its own run, from pos / slot). A run at position 0 starts from zero state. ---- */

@@ -111,6 +111,17 @@ def ptr(t: torch.Tensor | None) -> ctypes.c_void_p:
     return ctypes.c_void_p(0 if t is None else t.data_ptr())
 
 
+_sm_counts: dict = {}
+
+
+def sm_count(device: torch.device) -> int:
+    """Multiprocessors of a CUDA device (cached: the property query is slow on a hot path)."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    if key not in _sm_counts:
+        _sm_counts[key] = torch.cuda.get_device_properties(key).multi_processor_count
+    return _sm_counts[key]
+
+
 def count_launch(n: int = 1) -> None:
     global launch_count
     launch_count += n

@@ -25,6 +25,7 @@ import torch
 from . import _native as nv
 
 vp, i32, i64, f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+SPLIT_MAX = 8                        # most CTAs that share one decode token's keys
 
 
 def talking_attention(q: torch.Tensor, cache_k: torch.Tensor, table: torch.Tensor, pos: torch.Tensor, slot: torch.Tensor,
@@ -49,11 +50,20 @@ def talking_attention(q: torch.Tensor, cache_k: torch.Tensor, table: torch.Tenso
             # token is a tile of one row; sizes the kernel does not take come back as "unsupported" and go to the
             # per-token kernel below
             fn = nv.proto("b200_talking_attn_mma", [vp, i64, vp, i64, vp, vp, i32, vp, vp, vp, i32, vp, vp, vp, vp, i32, i32, i32, i32,
-                                                    f32, i32, vp])
+                                                    f32, i32, vp, i32, vp])
             tiles, n = (pieces.tiles, pieces.n_tiles) if pieces is not None else (None, T)
+            # a decode batch smaller than the machine: a token's keys are shared out over several CTAs (at least four
+            # chunks of 32 keys each) and merged by a second kernel; the count depends on static sizes only, so a captured
+            # graph replays it
+            nsplit, part = 1, None
+            if pieces is None:
+                keys = window if window > 0 else table.shape[1] * BS
+                nsplit = max(1, min(SPLIT_MAX, nv.sm_count(q.device) // T, (keys // 32 + 1) // 4))
+                if nsplit > 1:
+                    part = torch.empty(T, nsplit, H, D + 2, dtype=torch.float32, device=q.device)
             rc = fn(nv.ptr(q), q.stride(0), nv.ptr(gate), gate.stride(0) if gate is not None else 0, nv.ptr(cache_k),
                     nv.ptr(tiles), n, nv.ptr(pos), nv.ptr(slot), nv.ptr(table), table.shape[1], nv.ptr(r1), nv.ptr(r2), nv.ptr(talk),
-                    nv.ptr(out), H, G, D, BS, float(scale), int(window), nv.stream())
+                    nv.ptr(out), H, G, D, BS, float(scale), int(window), nv.ptr(part), nsplit, nv.stream())
             if rc == 0:
                 nv.count_launch()
                 return out

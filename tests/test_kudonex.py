@@ -429,6 +429,30 @@ def test_talking_attention_tokens_and_pieces(device, dtype, H, G, D, window):
 
 
 @pytest.mark.parametrize("device,dtype", CASES)
+@pytest.mark.parametrize("H,G,D,window", [(4, 2, 32, 0), (16, 4, 64, 300), (6, 3, 48, 1000), (5, 1, 16, 0)])
+def test_talking_attention_few_tokens_over_long_contexts(device, dtype, H, G, D, window):
+    """A handful of decode tokens over a long cache row: the 16-bit kernel shares a token's keys out over several CTAs and
+    merges their partial softmaxes. Tokens near the start (most CTAs get no key at all), at chunk and page borders and at
+    the end of the row, alone and as a batch, agree with the oracle and with each other."""
+    from llm_in_practise_b200.ops.talking_attention import talking_attention
+    n_pos = 1100
+    scale = D ** -0.5
+    cache, q, k, gate, r1, r2, talk = _attn_setup(device, dtype, H, G, D, n_pos, window, seed=3 * H + D)
+    dv = lambda t: t.to(device)                                     # noqa: E731
+    rows = [0, 1, 31, 32, 33, 127, 128, 129, 255, 256, 700, 1023, 1024, 1099]
+    want = _attn_oracle(q, k, gate, r1, r2, talk, H, G, D, scale, window, rows)
+    got = talking_attention(dv(q)[rows], cache.k[0], cache.table, _i32(rows, device), _i32([1] * len(rows), device), H, G, D, scale,
+                            window, dv(r1), dv(r2), dv(talk), gate=dv(gate)[rows])
+    e = row_errs(got, want)
+    assert float(e.max()) < tol(dtype), (float(e.max()), rows[int(e.argmax())])
+    for x in (0, 4, 9, 13):                                         # one token alone: the most CTAs per token
+        one = talking_attention(dv(q)[rows[x]:rows[x] + 1], cache.k[0], cache.table, _i32(rows[x:x + 1], device), _i32([1], device),
+                                H, G, D, scale, window, dv(r1), dv(r2), dv(talk), gate=dv(gate)[rows[x]:rows[x] + 1])
+        assert float(row_errs(one, want[x:x + 1]).max()) < tol(dtype), rows[x]
+        assert float((one.float() - got[x:x + 1].float()).abs().max()) < (1e-5 if dtype == torch.float32 else 0.04), rows[x]
+
+
+@pytest.mark.parametrize("device,dtype", CASES)
 @pytest.mark.parametrize("as_piece", [False, True])
 def test_one_dominant_key_at_the_window_edges(device, dtype, as_piece):
     """One key is made to dominate a query's scores. Inside the window (its far edge, a page border, the query's own
