@@ -179,9 +179,12 @@ def kernel_rows(size, dev, steps, warmup, root):
              steps, warmup)
     qd2 = torch.randn(T, H * 2 * Dm, device=dev).to(bf)
     ms_d = t(lambda: multimap_attention(qd2, dk, dv_, table, pos, slot, H, G, 2, Dm, D, Dm ** -0.5, win, 4, True, 0.4, 0.7, 1e-6, pieces), steps, warmup)
-    rows.append((f"prompt attention, window {win}, head mixing (mma.sync + fp32 mixing)", ms_k, frac_fl(4 * H * D * seen, ms_k),
+    # the mixing is H fp32 FMAs per score, which the design wants in 32 bits: at these sizes it takes the CUDA cores longer
+    # (at their nominal rate) than both products take the tensor cores, so it is the kernel's roofline
+    roof_k = max(frac_fl(4 * H * D * seen, ms_k), frac_fma(2 * H * H * seen, ms_k))
+    rows.append((f"prompt attention, window {win}, head mixing (mma.sync + fp32 mixing)", ms_k, roof_k,
                  f"Duratar: prompt attention, 2 maps, window {win} + 4 kept (mma.sync)", ms_d, frac_fl(2 * H * 2 * (Dm + D) * (seen + 4 * T), ms_d),
-                 "bf16 tensor"))
+                 "slower of bf16 tensor and fp32 FMA (mixing); Duratar: bf16 tensor"))
     # --- decode attention: 64 sequences at context 4032
     Bq, ctx = 64, 4032
     nbd = Bq * (ctx // BS + 1)

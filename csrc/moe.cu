@@ -9,6 +9,7 @@
 //                      whose `group_top` largest choice scores sum highest; the weights are s of the chosen experts, as
 //                      they are or renormalised to sum 1. Rows of W_r past the experts are per-token gates: their sigmoid
 //                      goes to gate_out (the gate of a shared expert). One warp per token; ties go to the lower index.
+//   b200_moe_dispatch  the expert-sorted, tile-padded row layout of the assignments (a stable counting sort in one launch).
 //   b200_moe_combine   out[t] = sum_k p[t, k] * y[dest[t * top + k]] (+ gate[t] * shared[t]) in fp32 (y: the expert-sorted
 //                      rows the grouped GEMM wrote), a fixed order of additions per token.
 #include "common.cuh"
@@ -184,6 +185,64 @@ moe_route_grouped_kernel(const TH* __restrict__ h, const TW* __restrict__ wr, co
     for (int k = 0; k < top; ++k) top_p[t * top + k] /= psum;
 }
 
+// Expert-sorted, tile-padded row layout of R = tokens * top assignments: dest[r] = first row of expert e's segment (segments
+// are padded to whole tiles) + the number of earlier assignments to e (a stable counting sort), tile_map[t] = expert of row
+// tile t or -1, counts[e], tok[r] = r / top. Every CTA counts all assignments (shared-memory atomics over a 16-bit copy of the
+// expert ids) and takes the prefix sums itself, so no CTA waits for another; then each warp places one expert's
+// assignments in order with ballots. CTA 0 also writes counts, tile_map and tok.
+__global__ void __launch_bounds__(256)
+moe_dispatch_kernel(const long long* __restrict__ top_i, long long* __restrict__ dest, long long* __restrict__ tok,
+                    int* __restrict__ tile_map, long long* __restrict__ counts, int R, int E, int top, int tile, int n_tiles) {
+  extern __shared__ __align__(16) unsigned char dsm[];
+  int* cnt = reinterpret_cast<int*>(dsm);                          // [E]
+  int* seg = cnt + E;                                              // [E + 1] first row of each expert's segment
+  unsigned short* ids = reinterpret_cast<unsigned short*>(seg + E + 1);   // [R]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int e = tid; e < E; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int r = tid; r < R; r += blockDim.x) {
+    const long long e = top_i[r];
+    const bool ok = e >= 0 && e < E;
+    ids[r] = ok ? (unsigned short)e : (unsigned short)0xffff;
+    if (ok) atomicAdd(&cnt[(int)e], 1);
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int at = 0;
+    for (int e = 0; e < E; ++e) {
+      seg[e] = at;
+      at += (cnt[e] + tile - 1) / tile * tile;
+    }
+    seg[E] = at;
+  }
+  __syncthreads();
+  const int e = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (e < E) {
+    int run = seg[e];
+    for (int r0 = 0; r0 < R; r0 += 32) {
+      const int r = r0 + lane;
+      const bool mine = r < R && ids[r] == (unsigned short)e;
+      const unsigned m = __ballot_sync(0xffffffffu, mine);
+      if (mine) dest[r] = run + __popc(m & ((1u << lane) - 1u));
+      run += __popc(m);
+    }
+  }
+  if (blockIdx.x != 0) return;
+  for (int x = tid; x < E; x += blockDim.x) counts[x] = cnt[x];
+  for (int r = tid; r < R; r += blockDim.x) tok[r] = r / top;
+  for (int t = tid; t < n_tiles; t += blockDim.x) {
+    const int row = t * tile;
+    int lo = 0, hi = E;                                            // the last expert whose segment starts at or before row
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (seg[mid] <= row) lo = mid; else hi = mid;
+    }
+    // empty experts have empty segments: step over them to the one that holds the row
+    while (lo + 1 < E && seg[lo + 1] <= row) ++lo;
+    tile_map[t] = row < seg[E] ? lo : -1;
+  }
+}
+
 template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ y, const long long* __restrict__ dest, const float* __restrict__ p,
                                    const T* __restrict__ shared, const float* __restrict__ gate, float* __restrict__ out,
@@ -245,6 +304,21 @@ B200_API int b200_moe_route_grouped(const void* h, const void* wr, const float* 
   else if (h_dtype == B200_DT_FP32 && w_dtype == B200_DT_BF16) RG(float, bf);
   else return B200_ERR_UNSUPPORTED;
 #undef RG
+  B200_LAUNCH_CHECK();
+  return 0;
+}
+
+B200_API int b200_moe_dispatch(const long long* top_i, long long* dest, long long* tok, int* tile_map, long long* counts,
+                               long long assignments, int E, int top, int tile, int n_tiles, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  if (assignments <= 0) return 0;
+  if (E <= 0 || E >= 0xffff || top <= 0 || tile <= 0 || n_tiles <= 0) return B200_ERR_BAD_SHAPE;
+  const size_t smem = (size_t)(2 * E + 1) * sizeof(int) + (size_t)assignments * sizeof(unsigned short);
+  if (smem > 200 * 1024) return B200_ERR_UNSUPPORTED;
+  if (smem > 48 * 1024) B200_CHECK(cudaFuncSetAttribute(moe_dispatch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const int warps = 8;
+  moe_dispatch_kernel<<<(E + warps - 1) / warps, warps * 32, smem, st>>>(top_i, dest, tok, tile_map, counts, (int)assignments, E,
+                                                                        top, tile, n_tiles);
   B200_LAUNCH_CHECK();
   return 0;
 }

@@ -119,11 +119,21 @@ talking_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, cons
   }
   for (int k = k_lo; k < k_hi; ++k) {
     const int j0 = chunk_j0(k);
-    __syncthreads();                                      // the previous chunk's keys and scores have been used (and Qs is there)
-    if (k + nbuf - 1 < k_hi) stage((k - k_lo + nbuf - 1) % nbuf, chunk_j0(k + nbuf - 1));
-    cp_async_commit();
-    cp_async_wait_upto<4>(nbuf - 1);
-    __syncthreads();
+    if (nbuf > 1) {
+      // this chunk's copies were issued nbuf - 1 iterations ago: wait for them, then one barrier both publishes them and
+      // says that the previous chunk's keys and scores have been used (and that Qs is there); only then is the buffer of
+      // the previous chunk refilled, while this chunk is worked on
+      cp_async_wait_upto<4>(nbuf - 2);
+      __syncthreads();
+      if (k + nbuf - 1 < k_hi) stage((k - k_lo + nbuf - 1) % nbuf, chunk_j0(k + nbuf - 1));
+      cp_async_commit();
+    } else {
+      __syncthreads();
+      stage(0, j0);
+      cp_async_commit();
+      cp_async_wait<0>();
+      __syncthreads();
+    }
     const __nv_bfloat16* Ks = Kbuf + ((k - k_lo) % nbuf) * kTmKeys * ldks;
     // the penalty depends on the head and on the distance only: the 47 distances a chunk's (row, key) pairs can have are
     // formed once per head here, not once per pair

@@ -498,6 +498,11 @@ int b200_moe_route(const void* h, const void* wr, const float* bias, long long* 
 int b200_moe_route_grouped(const void* h, const void* wr, const float* corr, long long* top_i, float* top_p, float* gate_out,
                            long long tokens, int W, int E, int X, int top, int groups, int keep, int group_top, int renorm,
                            int softmax, int h_dtype, int w_dtype, void* stream);
+/* Expert-sorted, tile-padded layout of the assignments top_i int64 [assignments] (= tokens * top): dest int64 [assignments],
+ * tok int64 [assignments] (= r / top), tile_map int32 [n_tiles] (expert of a row tile, -1 past the last), counts int64 [E].
+ * B200_ERR_UNSUPPORTED when the ids do not fit in shared memory (about 100k assignments). */
+int b200_moe_dispatch(const long long* top_i, long long* dest, long long* tok, int* tile_map, long long* counts,
+                      long long assignments, int E, int top, int tile, int n_tiles, void* stream);
 /* out fp32 [tokens, W] = sum_k p[t, k] * y[dest[t * top + k]] (y: expert-sorted rows of a grouped GEMM), plus
  * gate[t] * shared[t] when shared ([tokens, W], y's dtype) is given (gate fp32 [tokens] or NULL = 1). */
 int b200_moe_combine(const void* y, const long long* dest, const float* p, const void* shared, const float* gate, float* out,

@@ -52,6 +52,20 @@ def dispatch(top_i: torch.Tensor, num_experts: int, tile: int = TILE) -> Dispatc
     R, E = T * k, num_experts
     dev = top_i.device
     flat_e = top_i.reshape(-1)
+    nt = (R + E * (tile - 1) + tile - 1) // tile
+    if R > 0 and top_i.dtype == torch.long and nv.use_native(top_i) and nv.has("b200_moe_dispatch"):
+        # one launch instead of the two dozen small ones below (a decode step is bound by its launches)
+        flat_e = flat_e.contiguous()
+        dest, tok = torch.empty(R, dtype=torch.long, device=dev), torch.empty(R, dtype=torch.long, device=dev)
+        tile_map, counts = torch.empty(nt, dtype=torch.int32, device=dev), torch.empty(E, dtype=torch.long, device=dev)
+        vp, i32, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+        fn = nv.proto("b200_moe_dispatch", [vp, vp, vp, vp, vp, i64, i32, i32, i32, i32, vp])
+        rc = fn(nv.ptr(flat_e), nv.ptr(dest), nv.ptr(tok), nv.ptr(tile_map), nv.ptr(counts), R, E, k, tile, nt, nv.stream())
+        if rc == 0:
+            nv.count_launch()
+            return _with_host_counts(Dispatch(dest, tok, tile_map, counts, nt * tile, E))
+        if rc != nv.ERR_UNSUPPORTED:
+            nv.check(rc, "moe_dispatch")
     counts = (flat_e.unsqueeze(1) == torch.arange(E, device=dev)).sum(0)      # bincount reads its maximum back: not capturable
     padc = (counts + (tile - 1)) // tile * tile
     seg_end = torch.cumsum(padc, 0)
@@ -62,14 +76,17 @@ def dispatch(top_i: torch.Tensor, num_experts: int, tile: int = TILE) -> Dispatc
     rank_in = torch.arange(R, device=dev) - start_unp.index_select(0, sorted_e)
     dest = torch.empty(R, dtype=torch.long, device=dev)
     dest.index_copy_(0, order, seg_start.index_select(0, sorted_e) + rank_in)
-    nt = (R + E * (tile - 1) + tile - 1) // tile
     tile_start = torch.arange(nt, device=dev) * tile
     e_of_tile = torch.searchsorted(seg_end, tile_start, right=True)
     tile_map = torch.where(tile_start < seg_end[-1], e_of_tile, torch.full_like(e_of_tile, -1)).to(torch.int32)
-    d = Dispatch(dest, torch.arange(R, device=dev) // k, tile_map, counts, nt * tile, E)
-    if dev.type == "cuda" and not torch.cuda.is_current_stream_capturing():
-        d.counts_host = torch.empty(E, dtype=counts.dtype, pin_memory=True)
-        d.counts_host.copy_(counts, non_blocking=True)
+    return _with_host_counts(Dispatch(dest, torch.arange(R, device=dev) // k, tile_map, counts, nt * tile, E))
+
+
+def _with_host_counts(d: Dispatch) -> Dispatch:
+    """Start the asynchronous copy of the per-expert counts to pinned host memory (not inside a graph capture)."""
+    if d.counts.device.type == "cuda" and not torch.cuda.is_current_stream_capturing():
+        d.counts_host = torch.empty(d.num_experts, dtype=d.counts.dtype, pin_memory=True)
+        d.counts_host.copy_(d.counts, non_blocking=True)
         d.ready = torch.cuda.Event()
         d.ready.record()
     return d

@@ -657,3 +657,39 @@ def test_graphed_train_step_matches_eager_and_trains_with_dropout():
         assert losses[-1] < 0.7 * losses[0] and len(set(round(v, 5) for v in losses)) > 25
     finally:
         nvm.check(nvm.proto("b200_set_graph_state", [ctypes.c_void_p])(None), "set_graph_state")
+
+
+@pytest.mark.parametrize("T,k,E,tile", [(1, 1, 1, 128), (32, 2, 8, 128), (37, 3, 5, 8), (700, 4, 64, 16), (4096, 2, 8, 128), (513, 6, 300, 32)])
+def test_moe_dispatch_kernel_matches_the_sorted_layout(T, k, E, tile, monkeypatch):
+    """The one-launch dispatch gives the layout of the stable sort by expert: destinations, tokens, tile map, counts; experts
+    that receive nothing (one is forced) take no tile."""
+    from llm_in_practise_b200.ops import _native as nv
+    from llm_in_practise_b200.ops import moe
+    g = torch.Generator().manual_seed(T + E)
+    top_i = torch.randint(0, E, (T, k), generator=g)
+    if E > 2:
+        top_i[top_i == 1] = E - 1                                    # expert 1 receives nothing
+    top_i = top_i.cuda()
+    got = moe.dispatch(top_i, E, tile)
+    real = nv.has
+    monkeypatch.setattr(nv, "has", lambda name: name != "b200_moe_dispatch" and real(name))
+    want = moe.dispatch(top_i, E, tile)
+    assert got.rows == want.rows and got.num_experts == want.num_experts
+    for a in ("dest", "tok", "tile_map", "counts"):
+        assert torch.equal(getattr(got, a), getattr(want, a)), a
+    assert got.host_counts() == want.counts.tolist()
+
+
+@pytest.mark.parametrize("W", [64, 100, 2048])
+@pytest.mark.parametrize("hd,wd", [(torch.bfloat16, torch.float32), (torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16)])
+def test_router_logits_any_width(W, hd, wd):
+    from llm_in_practise_b200.ops.moe import ROUTE_SOFTMAX_ALL, route_grouped, route_topk
+    g = torch.Generator().manual_seed(W)
+    T, E, top = 77, 11, 3
+    h = torch.randn(T, W, generator=g).to(hd).cuda()
+    w = (torch.randn(E, W, generator=g) * W ** -0.5 * 3).to(wd).cuda()
+    s = torch.softmax(h.double() @ w.double().T, -1)
+    wp, wi = torch.topk(s, top, dim=-1)
+    for ti, tp in (route_topk(h, w, None, top, ROUTE_SOFTMAX_ALL)[:2], route_grouped(h, w, None, top, 1, 1, 1, softmax=True)[:2]):
+        assert torch.equal(ti, wi)
+        assert torch.allclose(tp.double(), wp, atol=1e-5, rtol=1e-4)
