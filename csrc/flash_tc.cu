@@ -239,7 +239,12 @@ flash_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm, const FlashTcParams 
       if (raise) { alpha = ex2f(m_ref - m_new); m_ref = m_new; }
       const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
       const bool any_raise = j > 0 && __any_sync(0xffffffffu, raise);
-      if (j > 0 && (!PT || any_raise)) {            // PV(j-1) complete: O is stable (and the shared P tile is free)
+      // PV(j-1) complete: O is stable (and the shared P tile is free). A parity wait tells phase c from c + 1, not from
+      // c + 2, and S(j) only proves PV(j-2) complete: a warp that skipped this wait for a while is still safe here (o_done has
+      // completed j - 1 or j phases), but it must not reach the wait after the loop two phases behind, where the parity of
+      // "PV(nblk-3) done" reads as "PV(nblk-1) done" and O would be taken before the last two products. So the last block
+      // always waits.
+      if (j > 0 && (!PT || any_raise || j == nblk - 1)) {
         mbar_wait_warp(o_done, (uint32_t)(j - 1) & 1u);
         tc_fence_after();
       }
