@@ -309,16 +309,16 @@ talking_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, cons
 }
 
 // out[t, h, :] = sum_s w_s o_s / sum_s w_s l_s, w_s = exp(m_s - max_s m_s), over the S partial walks of a token; then the gate.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(128)
 talking_attn_merge_kernel(const float* __restrict__ part, const __nv_bfloat16* __restrict__ gate, long long ldg,
                           __nv_bfloat16* __restrict__ out, int H, int D, int S) {
   const long long t = blockIdx.x;
-  for (int idx = threadIdx.x; idx < H * D; idx += blockDim.x) {
-    const int h = idx / D, d = idx - h * D;
-    const float* p = part + ((t * S) * H + h) * (D + 2);
-    const long long ss = (long long)H * (D + 2);
-    float M = -INFINITY;
-    for (int s = 0; s < S; ++s) M = fmaxf(M, p[s * ss + D]);
+  const int h = blockIdx.y;
+  const float* p = part + ((t * S) * H + h) * (D + 2);
+  const long long ss = (long long)H * (D + 2);
+  float M = -INFINITY;
+  for (int s = 0; s < S; ++s) M = fmaxf(M, p[s * ss + D]);
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
     float num = 0.f, den = 0.f;
     for (int s = 0; s < S; ++s) {
       const float m = p[s * ss + D];
@@ -327,6 +327,7 @@ talking_attn_merge_kernel(const float* __restrict__ part, const __nv_bfloat16* _
       den = fmaf(w, p[s * ss + D + 1], den);
     }
     float v = num / den;
+    const long long idx = (long long)h * D + d;
     if (gate) v *= 1.f / (1.f + expf(-__bfloat162float(gate[t * ldg + idx])));
     out[t * (long long)(H * D) + idx] = __float2bfloat16(v);
   }
@@ -385,7 +386,7 @@ B200_API int b200_talking_attn_mma(const void* q, long long ldq, const void* gat
 #undef TMMA_K
   B200_LAUNCH_CHECK();
   if (pw) {
-    talking_attn_merge_kernel<<<n_tiles, 256, 0, st>>>(pw, (const bf*)gate, ldg, (bf*)out, H, D, nsplit);
+    talking_attn_merge_kernel<<<dim3(n_tiles, H), D >= 128 ? 128 : (D > 32 ? 64 : 32), 0, st>>>(pw, (const bf*)gate, ldg, (bf*)out, H, D, nsplit);
     B200_LAUNCH_CHECK();
   }
   return 0;
