@@ -44,7 +44,7 @@ def parse_args():
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (result is then marked invalid)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--sequential-accum", action="store_true",
-                    help="run the micro-batches one after the other (round-1 schedule) instead of one layer-major pass")
+                    help="run the micro-batches one after the other (the earlier schedule) instead of one layer-major pass")
     ap.add_argument("--local_rank", type=int, default=-1)
     ap.add_argument("--workload", default="headline", choices=["headline", "gorozen", "segorax", "duratar", "kudonex"],
                     help="gorozen: prefill / decode throughput and kernel rooflines of the Gorozen design beside Qwen3 at equal "

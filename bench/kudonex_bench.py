@@ -211,7 +211,7 @@ def kernel_rows(size, dev, steps, warmup, root):
     aa, bb = torch.randn(T, SH * SD, device=dev), torch.randn(T, SH, device=dev)
     dtb, alog = torch.zeros(SH * SD, device=dev), torch.zeros(SH, device=dev)
     ms_d = t(lambda: delta_gates(qs, ks, aa, bb, dtb, alog, SG, SH, SD, 1.0), steps, warmup)
-    rows.append((f"mLSTM gates + running maximum, one prompt of {T} tokens (a walk in order)", ms_k, frac_bw(T * SH * 20, ms_k),
+    rows.append((f"mLSTM gates + running maximum, one prompt of {T} tokens (max-plus scans, 256 tokens per round)", ms_k, frac_bw(T * SH * 20, ms_k),
                  "Duratar: unit q / k, decays, beta (no recurrence)", ms_d, frac_bw(T * (2 * SG * SD + SH * SD + SH) * 8, ms_d), "HBM"))
     ms_k = t(lambda: ssm_gates(gi[:, :SH], bi, bi), steps, warmup)
     rows.append(("state-space step sizes and decays", ms_k, frac_bw(T * SH * 12, ms_k), None, 0.0, 0.0, "HBM"))

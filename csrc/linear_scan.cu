@@ -339,14 +339,13 @@ linear_scan_kernel(const float* __restrict__ q, long long ldq, const float* __re
   }
 }
 
-// One warp per (run, head). The gates of 32 tokens are formed in parallel; the maximum recurrence itself is walked in order
-// by every lane (two dependent operations per token), and lane j keeps what token j needs.
+// One warp per (run, head), a lane per token of a chunk of 32: the gates are formed in parallel and the maximum recurrence
+// m_t = max(f_t + m_(t-1), i_t) is a warp scan over max-plus maps; the maximum is carried from chunk to chunk.
 __global__ void __launch_bounds__(128)
 mlstm_gates_kernel(const float* __restrict__ gi, long long ldi, const float* __restrict__ gf, long long ldf,
                    const float* __restrict__ bi, const float* __restrict__ bf, float cap, float* __restrict__ mstate,
                    const int* __restrict__ runs, const int* __restrict__ pos, const int* __restrict__ slot, int n_runs, int H,
                    float* __restrict__ a, float* __restrict__ b, float* __restrict__ e) {
-  __shared__ float fs[4][32], is[4][32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long w = (long long)blockIdx.x * 4 + warp;
   if (w >= (long long)n_runs * H) return;
@@ -372,25 +371,81 @@ mlstm_gates_kernel(const float* __restrict__ gi, long long ldi, const float* __r
       const float z = cap * tanhf((gfc + bfh) / cap);
       fv = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));        // log sigmoid(z)
     }
-    fs[warp][lane] = fv;
-    is[warp][lane] = iv;
-    __syncwarp();
-    float mprev = 0.f, mnew = 0.f;
-#pragma unroll 8
-    for (int j = 0; j < cn; ++j) {
-      const float nm = fmaxf(fs[warp][j] + m, is[warp][j]);
-      if (j == lane) { mprev = m; mnew = nm; }
-      m = nm;
+    // token j maps the running maximum x to max(x + f_j, i_j); two such maps compose to one of the same form,
+    // (A1, B1) then (A2, B2) = (A1 + A2, max(B1 + A2, B2)), so the 32 tokens of a chunk are a warp scan of five steps
+    // instead of 32 dependent ones. Lanes past the chunk hold the identity (0, -inf). How the sums are rounded does not
+    // matter downstream: decay and input scale below are formed from the same maxima.
+    float A = lane < cn ? fv : 0.f, B = lane < cn ? iv : -INFINITY;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const float Ap = __shfl_up_sync(0xffffffffu, A, d), Bp = __shfl_up_sync(0xffffffffu, B, d);
+      if (lane >= d) { B = fmaxf(Bp + A, B); A = Ap + A; }
     }
+    const float mnew = fmaxf(m + A, B);
+    float mprev = __shfl_up_sync(0xffffffffu, mnew, 1);
+    if (lane == 0) mprev = m;
     if (lane < cn) {
       const long long t = first + c0 + lane;
       a[t * H + h] = expf(fv + mprev - mnew);
       b[t * H + h] = expf(iv - mnew);
       e[t * H + h] = expf(-mnew);
     }
-    __syncwarp();
+    m = __shfl_sync(0xffffffffu, mnew, cn - 1);
   }
   if (lane == 0) mstate[(long long)s * H + h] = m;
+}
+
+// The same for runs of many tokens: a CTA of eight warps per (run, head) takes 256 tokens per round. Every warp scans its
+// chunk of 32 without knowing the incoming maximum (the composite map of a chunk does not depend on it), leaves the
+// chunk's composite in shared memory, and then walks the composites of the chunks before it (at most seven steps) to get
+// its own incoming maximum.
+__global__ void __launch_bounds__(256)
+mlstm_gates_run_kernel(const float* __restrict__ gi, long long ldi, const float* __restrict__ gf, long long ldf,
+                       const float* __restrict__ bi, const float* __restrict__ bf, float cap, float* __restrict__ mstate,
+                       const int* __restrict__ runs, int H, float* __restrict__ a, float* __restrict__ b, float* __restrict__ e) {
+  __shared__ float cA[8], cB[8];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = blockIdx.x / H, h = blockIdx.x - r * H;
+  const int first = runs[4 * r], n = runs[4 * r + 1], p0 = runs[4 * r + 2], s = runs[4 * r + 3];
+  float m = p0 > 0 ? mstate[(long long)s * H + h] : 0.f;
+  const float bih = bi[h], bfh = bf[h];
+  for (int c0 = 0; c0 < n; c0 += 256) {
+    const int t0 = c0 + warp * 32;
+    const int cn = max(0, min(32, n - t0));
+    float fv = 0.f, iv = 0.f;
+    if (lane < cn) {
+      const long long t = first + t0 + lane;
+      iv = cap * tanhf((gi[t * ldi + h] + bih) / cap);
+      const float z = cap * tanhf((gf[t * ldf + h] + bfh) / cap);
+      fv = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));        // log sigmoid(z)
+    }
+    float A = lane < cn ? fv : 0.f, B = lane < cn ? iv : -INFINITY;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const float Ap = __shfl_up_sync(0xffffffffu, A, d), Bp = __shfl_up_sync(0xffffffffu, B, d);
+      if (lane >= d) { B = fmaxf(Bp + A, B); A = Ap + A; }
+    }
+    if (lane == 31) { cA[warp] = A; cB[warp] = B; }
+    __syncthreads();
+    float min_ = m, mend = m;
+#pragma unroll
+    for (int w2 = 0; w2 < 8; ++w2) {
+      if (w2 == warp) min_ = mend;
+      mend = fmaxf(mend + cA[w2], cB[w2]);
+    }
+    const float mnew = fmaxf(min_ + A, B);
+    float mprev = __shfl_up_sync(0xffffffffu, mnew, 1);
+    if (lane == 0) mprev = min_;
+    if (lane < cn) {
+      const long long t = first + t0 + lane;
+      a[t * H + h] = expf(fv + mprev - mnew);
+      b[t * H + h] = expf(iv - mnew);
+      e[t * H + h] = expf(-mnew);
+    }
+    m = mend;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) mstate[(long long)s * H + h] = m;
 }
 
 __global__ void ssm_gates_kernel(const float* __restrict__ dt, long long ld, const float* __restrict__ dt_bias,
@@ -557,6 +612,12 @@ B200_API int b200_mlstm_gates(const float* gi, long long ldi, const float* gf, l
   if (n_runs <= 0) return 0;
   if (H <= 0 || !(cap > 0.f)) return B200_ERR_BAD_SHAPE;
   const long long warps = (long long)n_runs * H;
+  if (runs) {                                              // pieces of prompts (and the single tokens beside them)
+    if (warps > 0x7fffffffLL) return B200_ERR_TOO_LARGE;
+    mlstm_gates_run_kernel<<<(unsigned)warps, 256, 0, (cudaStream_t)stream>>>(gi, ldi, gf, ldf, bi, bf, cap, mstate, runs, H, a, b, e);
+    B200_LAUNCH_CHECK();
+    return 0;
+  }
   mlstm_gates_kernel<<<(unsigned)((warps + 3) / 4), 128, 0, (cudaStream_t)stream>>>(gi, ldi, gf, ldf, bi, bf, cap, mstate, runs, pos,
                                                                                     slot, n_runs, H, a, b, e);
   B200_LAUNCH_CHECK();

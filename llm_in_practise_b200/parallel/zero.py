@@ -110,7 +110,7 @@ class ShardPrefetcher:
     computes, layer L+1's (backward: L-1's) shards — packed codes and scales, one contiguous range per owner — are
     copied out of the owners' memory into one of two local staging buffers by the COPY ENGINES (one ``cudaMemcpyAsync``
     per owner on a side stream), so the pull takes no SM away from the persistent GEMMs and the dequant kernels read
-    local HBM instead of stalling on NVLink latency. ``B200_PREFETCH_SM=1`` restores the SM pull kernel (the round-1
+    local HBM instead of stalling on NVLink latency. ``B200_PREFETCH_SM=1`` restores the SM pull kernel (the first
     path: measured 29 ms of exposed time per step at 8 GPUs because it shares SMs and shared memory with the GEMMs).
 
     ``exposed_ms()``: time the consuming stream sat in the wait for a prefetch (CUDA event pairs around every wait)."""

@@ -1,4 +1,4 @@
-"""Checkpoint formats pinned against the real libraries that are in the image (VERDICT round 1, item 12):
+"""Checkpoint formats pinned against the real libraries that are in the image:
 
 * compressed-tensors ``pack-quantized``: the ``compressed_tensors`` package itself quantises / packs / unpacks a weight, and
   this framework must read its tensors and produce tensors it reads back, to the bit.

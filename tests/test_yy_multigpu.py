@@ -224,7 +224,7 @@ def test_rank_skew_does_not_change_results(runs, plain, skewed):
 @multi
 def test_dense_zero3_memory_falls_with_world_size(runs):
     """ZeRO-3 of a dense model: what stays allocated per rank after a step (fp32 master shards + AdamW state) shrinks with
-    the world size (the round-1 engine kept full fp32 parameters and gradients on every rank)."""
+    the world size (an engine that keeps full fp32 parameters and gradients on every rank)."""
     a, b = runs["multi"]["dense3"], runs["single"]["dense3"]
     assert a["dense_sharded"] and a["ranks_identical"]
     assert a["persistent_bytes_per_rank"] < 0.75 * b["persistent_bytes_per_rank"], (a, b)
