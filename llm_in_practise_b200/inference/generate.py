@@ -28,6 +28,7 @@ from ..ops import fused_decode
 from ..ops.attention import attention
 from ..ops.gemm import ensure_graph_workspace, gemm, gemv16
 from ..ops.norm import rms_norm
+from ..utils.graph_step import no_gc
 
 vp, i32, f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
 _SPLIT_DECODE = __import__("os").environ.get("B200_DECODE_SPLIT", "1") != "0"
@@ -383,7 +384,7 @@ class Generator:
             self._prefill_packed_core(st["ids"], st["pos"], st["row"], st["cu"], st["last"], Tb, cache)   # warm-up
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
+            with no_gc(), torch.cuda.graph(graph):
                 st["logits"] = self._prefill_packed_core(st["ids"], st["pos"], st["row"], st["cu"], st["last"], Tb, cache)
             g = self._graphs[key] = (graph, st)
         graph, st = g
@@ -494,7 +495,7 @@ class Generator:
             self._decode(st["tok"], cache, st["pos"], st["slots"])          # warm-up: allocates every lazily built buffer
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
+            with no_gc(), torch.cuda.graph(graph):
                 st["logits"] = self._decode(st["tok"], cache, st["pos"], st["slots"])
             g = self._graphs[key] = (graph, st)
             cache.len = L

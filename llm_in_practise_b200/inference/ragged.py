@@ -19,6 +19,7 @@ from typing import List, Optional, Sequence, Tuple
 import torch
 
 from ..ops.gemm import ensure_graph_workspace
+from ..utils.graph_step import no_gc
 
 from .generate import GenerationConfig, Generator, PagedKVCache, sample_next
 
@@ -169,7 +170,7 @@ class RaggedGenerator(Generator):
             self.model.forward_ragged(st["ids"], st["pos"], st["slot"], cache, None, max_pos=mp - 1)       # warm-up: lazily built buffers
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
+            with no_gc(), torch.cuda.graph(graph):
                 st["logits"] = self.model.forward_ragged(st["ids"], st["pos"], st["slot"], cache, None, max_pos=mp - 1)
             g = graphs[key] = (graph, st)
         graph, st = g

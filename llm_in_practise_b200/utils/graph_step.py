@@ -16,12 +16,27 @@ step does not read anything back to the host (the framework's losses normalise o
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
+import gc
 from typing import Callable, Optional, Sequence
 
 import torch
 
 from ..ops import _native as nv
+
+
+@contextlib.contextmanager
+def no_gc():
+    """Keep the cyclic garbage collector out of a graph capture: a collection that happens to run inside it may destroy
+    earlier graphs, events or pinned buffers, and the driver calls of those destructors invalidate the capture."""
+    was = gc.isenabled()
+    gc.disable()
+    try:
+        yield
+    finally:
+        if was:
+            gc.enable()
 
 _SEED_STRIDE = 0x9E3779B97F4A7C15 & 0x7FFFFFFFFFFFFFFF
 _keep = []          # the registered seed-offset tensors must outlive every kernel that may read them
@@ -55,7 +70,7 @@ class GraphedTrainStep:
         torch.cuda.synchronize(dev)
         self.graph = torch.cuda.CUDAGraph()
         step_before = getattr(optimizer, "_step", None)
-        with torch.cuda.graph(self.graph):
+        with no_gc(), torch.cuda.graph(self.graph):
             self.loss = self._body()
         if step_before is not None:
             optimizer._step = step_before          # capture records the step, it does not run it
