@@ -27,7 +27,7 @@ __global__ void __launch_bounds__(kTalkThreads)
 talking_attn_kernel(const T* __restrict__ q, long long ldq, const T* __restrict__ gate, long long ldg, const T* __restrict__ ck,
                     const int* __restrict__ table, int max_blocks, const int* __restrict__ pos, const int* __restrict__ slot,
                     const float* __restrict__ r1, const float* __restrict__ r2, const float* __restrict__ talk,
-                    T* __restrict__ out, int H, int G, int D, int bs_log2, float scale, int window) {
+                    T* __restrict__ out, int H, int G, int D, int bs_log2, float scale, int window, int chunk) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int t = blockIdx.x;
   const int i = pos[t], s = slot[t];
@@ -55,8 +55,8 @@ talking_attn_kernel(const T* __restrict__ q, long long ldq, const T* __restrict_
   for (int u = 0; u < U; ++u) acc[u] = 0.f;
   const int* trow = table + (long long)s * max_blocks;
 
-  for (int j0 = lo; j0 <= i; j0 += kTalkChunk) {
-    const int cn = min(kTalkChunk, i + 1 - j0);
+  for (int j0 = lo; j0 <= i; j0 += chunk) {               // chunk <= 32 keys: fewer when many wide kv heads fill shared memory
+    const int cn = min(chunk, i + 1 - j0);
     __syncthreads();                                      // the previous chunk's keys and weights have been used
     // ---- stage the chunk's key rows (all kv heads of a position side by side)
     for (int e = threadIdx.x; e < cn * GD; e += kTalkThreads) {
@@ -129,7 +129,10 @@ static int talking_launch(const void* q, long long ldq, const void* gate, long l
   const int HD = H * D;
   const int ldk = G * D + (sizeof(T) == 2 ? 2 : 1), ldr = kTalkChunk + 1;
   const int nf = HD + 2 * H * ldr + H * H + 3 * H;
-  const size_t smem = ((size_t)((nf + 3) & ~3)) * 4 + (size_t)kTalkChunk * ldk * sizeof(T);
+  const size_t fixed = ((size_t)((nf + 3) & ~3)) * 4;
+  int chunk = kTalkChunk;                                  // as many keys per chunk as fit beside the query and the scores
+  while (chunk > 1 && fixed + (size_t)chunk * ldk * sizeof(T) > 200 * 1024) chunk >>= 1;
+  const size_t smem = fixed + (size_t)chunk * ldk * sizeof(T);
   if (smem > 200 * 1024 || HD > 32 * kTalkThreads) return B200_ERR_TOO_LARGE;
   const int U = (HD + kTalkThreads - 1) / kTalkThreads;
 #define TALK(UU)                                                                                                            \
@@ -137,7 +140,7 @@ static int talking_launch(const void* q, long long ldq, const void* gate, long l
     auto kern = talking_attn_kernel<T, UU>;                                                                                 \
     if (smem > 48 * 1024) B200_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));   \
     kern<<<tokens, kTalkThreads, smem, st>>>((const T*)q, ldq, (const T*)gate, ldg, (const T*)ck, table, max_blocks, pos, slot, \
-                                             r1, r2, talk, (T*)out, H, G, D, bs_log2, scale, window);                       \
+                                             r1, r2, talk, (T*)out, H, G, D, bs_log2, scale, window, chunk);                \
   } while (0)
   if (U <= 2) TALK(2); else if (U <= 4) TALK(4); else if (U <= 8) TALK(8); else if (U <= 16) TALK(16); else TALK(32);
 #undef TALK

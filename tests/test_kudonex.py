@@ -402,7 +402,8 @@ def _attn_oracle(q, k, gate, r1, r2, talk, H, G, D, scale, window, rows):
 
 
 @pytest.mark.parametrize("device,dtype", CASES)
-@pytest.mark.parametrize("H,G,D,window", [(4, 2, 16, 40), (6, 1, 20, 33), (2, 2, 32, 1), (8, 4, 64, 72), (3, 3, 24, 0), (16, 2, 128, 100)])
+@pytest.mark.parametrize("H,G,D,window", [(4, 2, 16, 40), (6, 1, 20, 33), (2, 2, 32, 1), (8, 4, 64, 72), (3, 3, 24, 0), (16, 2, 128, 100),
+                                           (16, 16, 96, 150)])          # the last: kv rows so wide that fewer keys are staged at a time
 def test_talking_attention_tokens_and_pieces(device, dtype, H, G, D, window):
     """Single tokens (decode) and prompt pieces that start in the middle of a page, against the oracle: distance penalty,
     head mixing, window, keys as values, output gate."""
